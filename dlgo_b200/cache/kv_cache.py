@@ -1,7 +1,7 @@
 """Device storage of the cache and its mirror of the page tables.
 
 Per group of run entries with equal needs, ONE allocation
-``[entries, 2 (keys, values), pages, kv_heads, page_size, head_dim]`` in the
+``[entries, planes (keys, values; or one for both), pages, kv_heads, page_size, head_dim]`` in the
 run's precision and one page table ``[slots, pages per sequence]`` (int32, -1
 where no page is held).  The layout keeps one kv head's 64 positions of a page
 contiguous, which is what the attention kernel streams.
@@ -89,12 +89,12 @@ class KVCache:
         for i, need in enumerate(entry_needs):
             if need is None or borrows[i] is not None:
                 continue
-            keyed.setdefault((need.group, need.num_kv_heads, need.head_dim, need.window), []).append(i)
+            keyed.setdefault((need.group, need.num_kv_heads, need.head_dim, need.window, need.planes), []).append(i)
         names: Dict[Tuple, str] = {}
         for key in keyed:
             base = key[0]
             clash = [k for k in keyed if k[0] == base]
-            names[key] = base if len(clash) == 1 else f"{base}/{key[1]}x{key[2]}w{key[3]}"
+            names[key] = base if len(clash) == 1 else f"{base}/{key[1]}x{key[2]}w{key[3]}" + ("" if key[4] == 2 else f"p{key[4]}")
         self.book = CacheBook([(names[k], k[3]) for k in keyed], n_pages, page_size, self.n_slots, self.max_seq_len)
         self._no_window = all(k[3] is None for k in keyed)
         self.storage: Dict[str, torch.Tensor] = {}
@@ -102,8 +102,9 @@ class KVCache:
         self._entry_place: Dict[int, Tuple[str, int]] = {}
         for key, entries in keyed.items():
             name = names[key]
-            _, hkv, hd, _ = key
-            self.storage[name] = torch.empty((len(entries), 2, n_pages, hkv, page_size, hd), dtype=dtype, device=device)
+            _, hkv, hd, _, planes = key
+            self.storage[name] = torch.empty((len(entries), planes, n_pages, hkv, page_size, hd), dtype=dtype,
+                                             device=device)
             self.page_tables[name] = torch.full((self.n_slots, self.book.max_pages_per_seq), -1, dtype=torch.int32,
                                                 device=device)
             for j, e in enumerate(entries):
@@ -122,7 +123,8 @@ class KVCache:
             return None
         name, j = place
         st = self.storage[name]
-        return CacheView(st[j, 0], st[j, 1], self.page_tables[name], self.page_size, writes=src == entry)
+        # (one plane: the rows serve as keys and as values)
+        return CacheView(st[j, 0], st[j, st.shape[1] - 1], self.page_tables[name], self.page_size, writes=src == entry)
 
     def bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.storage.values())

@@ -3,8 +3,9 @@ from .registry import (ConfigError, config_class_for, config_from_dict, load_con
                        register_architecture, registered_architectures)
 from .spec import ArchitectureSpec, LayerSpec, PartSpec, RunEntry
 from .llama import LlamaConfig, RopeScaling
+from .dedutar import DedutarConfig
 
 __all__ = [
-    "ArchitectureSpec", "ConfigError", "LayerSpec", "LlamaConfig", "PartSpec", "RopeScaling", "RunEntry",
+    "ArchitectureSpec", "ConfigError", "DedutarConfig", "LayerSpec", "LlamaConfig", "PartSpec", "RopeScaling", "RunEntry",
     "config_class_for", "config_from_dict", "load_config", "register_architecture", "registered_architectures",
 ]

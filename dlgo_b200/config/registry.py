@@ -52,11 +52,11 @@ def config_class_for(name: str) -> Any:
 
 
 def config_from_dict(d: Mapping[str, Any]) -> ArchitectureConfig:
-    archs = d.get("architectures")
+    archs = d.get("architectures", d.get("architecture"))      # a list of names, or one name under either key
     if isinstance(archs, str):
         archs = [archs]
     if not archs or not isinstance(archs, (list, tuple)):
-        raise ConfigError('config.json has no "architectures" entry')
+        raise ConfigError('config.json has no "architectures" (or "architecture") entry')
     cls = config_class_for(str(archs[0]))
     return cls.from_dict(d)
 

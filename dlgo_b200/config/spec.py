@@ -51,10 +51,13 @@ class LayerSpec:
     ffn: Optional[PartSpec]
     norms: Mapping[str, PartSpec]
     names: Mapping[str, str]
+    # parts of the arrangement itself that hold tensors (the read/write coefficients of a block with several
+    # residual streams, one per sublayer): role -> part, named like the norms
+    connections: Mapping[str, PartSpec] = field(default_factory=dict)
 
     def roles(self) -> Sequence[str]:
         """Every role of the layer that has a part, norms first in their own order."""
-        out = list(self.norms)
+        out = list(self.norms) + list(self.connections)
         if self.mixer is not None:
             out.append("mixer")
         if self.ffn is not None:
@@ -93,6 +96,9 @@ class ArchitectureSpec:
     position_encodings: Mapping[str, PartSpec]
     bos_token_id: Optional[int]
     stop_token_ids: Sequence[int]
+    # residual streams: ``None`` is the usual single stream [tokens, hidden]; a number s (1 included) makes the
+    # stream [tokens, s, hidden], every copy equal to the embedding at the start and summed before the final norm
+    streams: Optional[int] = None
 
     def validate(self) -> None:
         n = len(self.layers)
@@ -104,8 +110,12 @@ class ArchitectureSpec:
             missing = [r for r in ls.roles() if r not in ls.names]
             if missing:
                 raise ValueError(f"layer {j}: no tensor-name prefix for the role(s) {', '.join(missing)}")
-            if set(ls.norms) & {"mixer", "ffn"}:
-                raise ValueError(f"layer {j}: a norm cannot take the role name 'mixer' or 'ffn'")
+            if (set(ls.norms) | set(ls.connections)) & {"mixer", "ffn"}:
+                raise ValueError(f"layer {j}: a norm or connection cannot take the role name 'mixer' or 'ffn'")
+            if set(ls.norms) & set(ls.connections):
+                raise ValueError(f"layer {j}: a role names both a norm and a connection")
+        if self.streams is not None and self.streams < 1:
+            raise ValueError(f"streams must be at least 1, got {self.streams}")
         for i, e in enumerate(self.order):
             if not 0 <= e.layer < n:
                 raise ValueError(f"run entry {i} names layer {e.layer}, but there are {n} layers")

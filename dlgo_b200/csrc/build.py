@@ -39,6 +39,9 @@ LIBRARIES: Dict[str, List[str]] = {
     "attention_prefill_tc": ["attention_prefill_tc.cu"],
     "decode_layers": ["decode_layers.cu"],
     "prompt_layers": ["prompt_layers.cu"],
+    "streams": ["streams.cu"],
+    "latent_attention": ["latent_attention.cu"],
+    "lightning": ["lightning.cu"],
 }
 _HEADERS = ["common.cuh", "attention_noalloc.h", "attention_combine.cuh", "attention_decode_tiles.cuh", "tcgen05.cuh"]
 

@@ -14,14 +14,22 @@ namespace dlgo {
 // ---------------------------------------------------------------- embedding
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
-                             float* __restrict__ out, int d, int vocab) {
+                             float* __restrict__ out, int d, int vocab, int copies) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
   int tok = tokens[t];
   const bool ok = tok >= 0 && tok < vocab;
   const TW* row = table + (size_t)(ok ? tok : 0) * d;
-  float* o = out + (size_t)t * d;
+  float* o = out + (size_t)t * d * copies;
+  if (copies > 1) {
+    // several residual streams: every copy starts as the embedding
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+      const float v = ok ? to_float(row[i]) : 0.f;
+      for (int c = 0; c < copies; ++c) o[(size_t)c * d + i] = v;
+    }
+    return;
+  }
   if (sizeof(TW) == 2 && (d & 7) == 0 && ((uintptr_t)table & 15) == 0) {
     // 16 bytes of the row per thread and trip: the whole row is in flight at once
     for (int i = threadIdx.x * 8; i < d; i += blockDim.x * 8) {
@@ -310,14 +318,14 @@ using namespace dlgo;
 
 // tokens[T] int32, table[vocab, d] (f32 or bf16), out[T, d] f32
 DLGO_EXPORT int dlgo_embed(const int* tokens, const void* table, int table_dtype, float* out, int T, int d,
-                           int vocab, cudaStream_t stream) {
+                           int vocab, int copies, cudaStream_t stream) {
   if (T <= 0) return DLGO_OK;
-  if (d <= 0 || vocab <= 0) return DLGO_ERR_SIZE;
+  if (d <= 0 || vocab <= 0 || copies < 1) return DLGO_ERR_SIZE;
   const int threads = d >= 1024 ? 256 : 128;
   if (table_dtype == DLGO_F32)
-    launch_kernel_first(embed_kernel<float>, dim3(T), dim3(threads), 0, stream, tokens, (const float*)table, out, d, vocab);
+    launch_kernel_first(embed_kernel<float>, dim3(T), dim3(threads), 0, stream, tokens, (const float*)table, out, d, vocab, copies);
   else if (table_dtype == DLGO_BF16)
-    launch_kernel_first(embed_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, tokens, (const __nv_bfloat16*)table, out, d, vocab);
+    launch_kernel_first(embed_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, tokens, (const __nv_bfloat16*)table, out, d, vocab, copies);
   else
     return DLGO_ERR_DTYPE;
   return launch_status();

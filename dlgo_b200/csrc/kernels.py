@@ -101,16 +101,17 @@ _i, _f, _p, _ll = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlo
 
 
 # ------------------------------------------------------------------ elementwise
-def embed(tokens: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[t, :] = table[tokens[t], :] as fp32."""
+def embed(tokens: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None,
+          copies: Optional[int] = None) -> torch.Tensor:
+    """out[t, :] = table[tokens[t], :] as fp32; with ``copies`` = s, out[t, c, :] for c < s (all equal)."""
     _need(tokens, torch.int32, "tokens")
     _need(table, None, "table")
     T, (V, d) = tokens.numel(), table.shape
     if out is None:
-        out = torch.empty((T, d), dtype=torch.float32, device=table.device)
+        out = torch.empty((T, d) if copies is None else (T, copies, d), dtype=torch.float32, device=table.device)
     _need(out, torch.float32, "out")
     st = _lib("elementwise").dlgo_embed(_ptr(tokens), _ptr(table), _i(dtype_code(table.dtype)), _ptr(out), _i(T), _i(d),
-                                        _i(V), _stream())
+                                        _i(V), _i(copies or 1), _stream())
     _check(st, "embed")
     return out
 
@@ -168,6 +169,184 @@ def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.T
     st = _lib("elementwise").dlgo_swiglu(_ptr(gate_up), _ptr(out), _i(dtype_code(gate_up.dtype)), _i(T), _i(F),
                                          _stream())
     _check(st, "swiglu")
+    return out
+
+
+# ----------------------------------------------- residual streams and their norms
+NORM_NONE, NORM_RMS, NORM_DYT = 0, 1, 2
+ACT_NONE, ACT_RELU2, ACT_SILU, ACT_GELU_TANH = 0, 1, 2, 3
+MAX_STREAMS = 8
+
+
+def streams_step(X: torch.Tensor, *, y: Optional[torch.Tensor] = None, y_bias: Optional[torch.Tensor] = None,
+                 mix: Optional[torch.Tensor] = None, write: Optional[torch.Tensor] = None, clear_y: bool = False,
+                 read: Optional[torch.Tensor] = None, norm_kind: int = NORM_NONE,
+                 norm_w: Optional[torch.Tensor] = None, norm_b: Optional[torch.Tensor] = None,
+                 norm_alpha: Optional[torch.Tensor] = None, eps: float = 0.0,
+                 out_dtype: Optional[torch.dtype] = None, rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """One hand-over on residual streams ``X`` [T, s, d] (fp32, in place).
+
+    Write part (with ``y`` [T, d] fp32): ``X[t, q] = sum_r mix[r, q] X[t, r] + write[q] * (y[t] + y_bias)``,
+    all streams at once from the old values; ``clear_y`` leaves zeros in ``y``.  Read part (with
+    ``out_dtype``): ``u = sum_r read[r] X[t, r]`` (``read`` None: the plain sum) through the norm
+    (``NORM_DYT``: tanh(alpha u) w + b; ``NORM_RMS``; ``NORM_NONE``: u itself) into a new [R, d] tensor;
+    ``rows`` picks the rows to read (read part only)."""
+    _need(X, torch.float32, "X")
+    if X.dim() != 3:
+        raise KernelError("streams_step: X must be [tokens, streams, hidden]")
+    T, s, d = X.shape
+    if s > MAX_STREAMS:
+        raise KernelError(f"streams_step: at most {MAX_STREAMS} streams, got {s}")
+    if y is not None:
+        _need(y, torch.float32, "y")
+        if tuple(y.shape) != (T, d) or mix is None or write is None or rows is not None:
+            raise KernelError("streams_step: the write part needs y [T, d], mix, write, and no row selection")
+        _need(mix, torch.float32, "mix")
+        _need(write, torch.float32, "write")
+        if tuple(mix.shape) != (s, s) or write.numel() != s:
+            raise KernelError("streams_step: mix must be [s, s] and write [s]")
+    for n, t in (("y_bias", y_bias), ("read", read), ("norm_w", norm_w), ("norm_b", norm_b), ("norm_alpha", norm_alpha)):
+        if t is not None:
+            _need(t, torch.float32, n)
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+    R = T if rows is None else rows.numel()
+    out = None
+    if out_dtype is not None:
+        if norm_kind != NORM_NONE and (norm_w is None or norm_w.numel() != d):
+            raise KernelError("streams_step: the norm needs a weight of the hidden size")
+        if norm_kind == NORM_DYT and norm_alpha is None:
+            raise KernelError("streams_step: Dynamic Tanh needs alpha")
+        out = torch.empty((R, d), dtype=out_dtype, device=X.device)
+    elif y is None:
+        return None
+    st = _lib("streams").dlgo_streams_step(
+        _ptr(X), _i(T), _i(s), _i(d), _ptr(y), _ptr(y_bias), _ptr(mix), _ptr(write), _i(1 if clear_y else 0),
+        _ptr(read), _i(norm_kind), _ptr(norm_w), _ptr(norm_b), _ptr(norm_alpha), _f(eps), _ptr(out),
+        _i(dtype_code(out_dtype) if out_dtype is not None else F32), _ptr(rows), _i(R), _stream())
+    _check(st, "streams_step")
+    return out
+
+
+def bias_act(z: torch.Tensor, bias: Optional[torch.Tensor], act: int, out_dtype: torch.dtype,
+             in_place: bool = False) -> torch.Tensor:
+    """``act(z + bias)`` for fp32 ``z`` [T, n] (unit inner stride), into ``out_dtype``; ``in_place`` (fp32) writes z."""
+    if z.dtype != torch.float32 or z.dim() != 2 or z.stride(1) != 1:
+        raise KernelError("bias_act: z must be 2-D float32 with unit inner stride")
+    T, n = z.shape
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+        if bias.numel() != n:
+            raise KernelError(f"bias_act: bias has {bias.numel()} elements, rows have {n}")
+    if in_place:
+        if out_dtype != torch.float32:
+            raise KernelError("bias_act: in place only in float32")
+        out = z
+    else:
+        out = torch.empty((T, n), dtype=out_dtype, device=z.device)
+    st = _lib("streams").dlgo_bias_act(_ptr(z), _i(z.stride(0)), _ptr(bias), _ptr(out), _i(dtype_code(out_dtype)),
+                                       _i(out.stride(0)), _i(T), _i(n), _i(act), _stream())
+    _check(st, "bias_act")
+    return out
+
+
+def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """``rms(o) * w * sigmoid(gate)`` row by row; o and gate are fp32 [T, n] views with unit inner stride."""
+    for n_, t in (("o", o), ("gate", gate)):
+        if t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1:
+            raise KernelError(f"gated_rmsnorm: {n_} must be 2-D float32 with unit inner stride")
+    _need(w, torch.float32, "w")
+    T, n = o.shape
+    if tuple(gate.shape) != (T, n) or w.numel() != n:
+        raise KernelError("gated_rmsnorm: shapes differ")
+    out = torch.empty((T, n), dtype=out_dtype, device=o.device)
+    st = _lib("streams").dlgo_gated_rmsnorm(_ptr(o), _i(o.stride(0)), _ptr(gate), _i(gate.stride(0)), _ptr(w), _ptr(out),
+                                            _i(dtype_code(out_dtype)), _i(T), _i(n), _f(eps), _stream())
+    _check(st, "gated_rmsnorm")
+    return out
+
+
+# ------------------------------------------------------------- latent attention
+def latent_norm_append(proj: torch.Tensor, kv_off: int, kv_rank: int, w_kv: torch.Tensor, q_off: int, q_rank: int,
+                       w_q: Optional[torch.Tensor], eps: float, token_pos: torch.Tensor, token_seq: torch.Tensor,
+                       seq_slot: torch.Tensor, page_table: torch.Tensor, pages: torch.Tensor,
+                       write_cache: bool = True) -> Optional[torch.Tensor]:
+    """RMS norms of the latents in fp32 ``proj`` [T, ld]: columns ``kv_off ...`` go (normed, times ``w_kv``) to
+    the paged cache ``pages`` [n, 1, page, kv_rank] at each token's position; with ``q_rank`` > 0 columns
+    ``q_off ...`` come back normed (times ``w_q``) as [T, q_rank] in the cache's type."""
+    if proj.dtype != torch.float32 or proj.dim() != 2 or proj.stride(1) != 1:
+        raise KernelError("latent_norm_append: proj must be 2-D float32 with unit inner stride")
+    _need(w_kv, torch.float32, "w_kv")
+    _need(pages, None, "pages")
+    for n, t in (("token_pos", token_pos), ("token_seq", token_seq), ("seq_slot", seq_slot), ("page_table", page_table)):
+        _need(t, torch.int32, n)
+    T = proj.shape[0]
+    if pages.shape[-1] != kv_rank or w_kv.numel() != kv_rank:
+        raise KernelError("latent_norm_append: the cache's rows and the norm weight must have kv_rank elements")
+    cq = None
+    if q_rank > 0:
+        _need(w_q, torch.float32, "w_q")
+        cq = torch.empty((T, q_rank), dtype=pages.dtype, device=proj.device)
+    st = _lib("latent_attention").dlgo_latent_norm_append(
+        _ptr(proj), _i(proj.stride(0)), _i(T), _i(kv_off), _i(kv_rank), _ptr(w_kv), _i(q_off), _i(q_rank), _ptr(w_q),
+        _ptr(cq), _f(eps), _ptr(token_pos), _ptr(token_seq), _ptr(seq_slot), _ptr(page_table), _i(page_table.shape[1]),
+        _ptr(pages), _i(dtype_code(pages.dtype)), _i(pages.shape[-2]), _i(1 if write_cache else 0), _stream())
+    _check(st, "latent_norm_append")
+    return cq
+
+
+def latent_attention(q: torch.Tensor, w_k: torch.Tensor, w_v: torch.Tensor, sink: Optional[torch.Tensor],
+                     pages: torch.Tensor, page_table: torch.Tensor, seq_slot: torch.Tensor, token_seq: torch.Tensor,
+                     token_pos: torch.Tensor, num_heads: int, qk_dim: int, v_dim: int, scale: float,
+                     window: int = 0) -> torch.Tensor:
+    """Causal attention of packed tokens over cached latents ``pages`` [n, 1, page, rank]: per head
+    ``softmax((Wk^T q) . c * scale) c`` carried out through ``Wv``; ``q`` [T, >= H*qk_dim] (fp32 or the cache's
+    type), ``w_k`` [H*qk_dim, rank], ``w_v`` [H*v_dim, rank] in the cache's type.  Returns [T, H*v_dim]."""
+    _need(pages, None, "pages")
+    _need(w_k, pages.dtype, "w_k")
+    _need(w_v, pages.dtype, "w_v")
+    if q.dtype not in (torch.float32, pages.dtype) or q.dim() != 2 or q.stride(1) != 1:
+        raise KernelError("latent_attention: q must be 2-D, float32 or the cache's type, with unit inner stride")
+    if sink is not None:
+        _need(sink, torch.float32, "sink")
+    for n, t in (("page_table", page_table), ("seq_slot", seq_slot), ("token_seq", token_seq), ("token_pos", token_pos)):
+        _need(t, torch.int32, n)
+    T, rank = q.shape[0], pages.shape[-1]
+    if tuple(w_k.shape) != (num_heads * qk_dim, rank) or tuple(w_v.shape) != (num_heads * v_dim, rank):
+        raise KernelError("latent_attention: the up-projections do not fit heads, sizes and rank")
+    out = torch.empty((T, num_heads * v_dim), dtype=pages.dtype, device=q.device)
+    st = _lib("latent_attention").dlgo_latent_attention(
+        _ptr(q), _i(1 if q.dtype == torch.float32 else 0), _i(q.stride(0)), _ptr(w_k), _ptr(w_v), _ptr(sink),
+        _ptr(pages), _i(dtype_code(pages.dtype)), _ptr(page_table), _i(page_table.shape[1]), _i(pages.shape[-2]),
+        _ptr(seq_slot), _ptr(token_seq), _ptr(token_pos), _ptr(out), _i(out.stride(0)), _i(T), _i(num_heads),
+        _i(qk_dim), _i(v_dim), _i(rank), _f(scale), _i(window), _stream())
+    _check(st, "latent_attention")
+    return out
+
+
+# ---------------------------------------------------------- lightning attention
+def lightning_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, tiles: torch.Tensor, n_seqs: int,
+                   seq_slot: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, num_heads: int, qk_dim: int,
+                   v_dim: int) -> torch.Tensor:
+    """Decayed linear attention of packed tokens, sequence by sequence in token order, continuing each
+    sequence's fp32 state ``state`` [slots, H, qk_dim, v_dim] (in place).  ``proj`` [T, ld] fp32 holds the
+    q, k and v projections at the given column offsets (silu is applied here); ``tiles`` [n_seqs, 3] lists
+    (sequence, first packed token, count).  Returns fp32 [T, H*v_dim]."""
+    if proj.dtype != torch.float32 or proj.dim() != 2 or proj.stride(1) != 1:
+        raise KernelError("lightning_scan: proj must be 2-D float32 with unit inner stride")
+    _need(tiles, torch.int32, "tiles")
+    _need(seq_slot, torch.int32, "seq_slot")
+    _need(decay, torch.float32, "decay")
+    _need(state, torch.float32, "state")
+    if tuple(state.shape[1:]) != (num_heads, qk_dim, v_dim) or decay.numel() != num_heads:
+        raise KernelError("lightning_scan: state must be [slots, heads, qk_dim, v_dim] and decay [heads]")
+    T = proj.shape[0]
+    out = torch.empty((T, num_heads * v_dim), dtype=torch.float32, device=proj.device)
+    st = _lib("lightning").dlgo_lightning_scan(_ptr(proj), _i(proj.stride(0)), _i(q_off), _i(k_off), _i(v_off),
+                                               _ptr(tiles), _i(n_seqs), _ptr(seq_slot), _ptr(decay), _ptr(state),
+                                               _ptr(out), _i(out.stride(0)), _i(num_heads), _i(qk_dim), _i(v_dim),
+                                               _stream())
+    _check(st, "lightning_scan")
     return out
 
 

@@ -68,7 +68,7 @@ class Engine:
         needs, borrows, states = self.model.cache_needs()
         if max_tokens is None or max_tokens <= 0:
             # room for `default_batch` sequences of full length, within half of the free memory
-            per_position = sum(2 * n.num_kv_heads * n.head_dim for n, b in zip(needs, borrows)
+            per_position = sum(n.planes * n.num_kv_heads * n.head_dim for n, b in zip(needs, borrows)
                                if n is not None and b is None) * (2 if self.runtime.dtype == torch.bfloat16 else 4)
             free, _ = torch.cuda.mem_get_info(self.runtime.device)
             fits = max(PAGE_SIZE, int(free * 0.5) // max(per_position, 1))

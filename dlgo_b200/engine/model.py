@@ -32,7 +32,13 @@ class CausalLM:
             mixer = R.MIXERS.build(ls.mixer) if ls.mixer is not None else None
             ffn = R.FEED_FORWARDS.build(ls.ffn) if ls.ffn is not None else None
             norms = {role: R.NORMS.build(ns) for role, ns in ls.norms.items()}
-            self.blocks.append(R.BLOCKS.build(PartSpec(ls.block, {"mixer": mixer, "ffn": ffn, "norms": norms})))
+            params = {"mixer": mixer, "ffn": ffn, "norms": norms}
+            if ls.connections:
+                params["connections"] = {role: R.CONNECTIONS.build(cs) for role, cs in ls.connections.items()}
+            self.blocks.append(R.BLOCKS.build(PartSpec(ls.block, params)))
+            if (spec.streams is not None) != bool(getattr(self.blocks[-1], "on_streams", False)):
+                raise ValueError(f"layer {len(self.blocks) - 1}: the block {ls.block!r} does not fit a model "
+                                 f"{'with' if spec.streams is not None else 'without'} residual streams")
         self.order = list(spec.order)
         for i, e in enumerate(self.order):
             if e.cache_of is not None:
@@ -108,7 +114,10 @@ class CausalLM:
     # ------------------------------------------------------------------ forward
     def forward(self, ctx: Any, cache: Any, want_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         """Run the step's tokens; logits [wanted, vocab] fp32 for the packed rows ``want_rows`` (int32)."""
-        residual = self.embedding.forward(ctx.token_ids)
+        streams = self.spec.streams
+        # one fp32 residual stream [T, hidden], or `streams` copies of it [T, streams, hidden]
+        residual = (self.embedding.forward(ctx.token_ids) if streams is None else
+                    self.embedding.forward(ctx.token_ids, copies=streams))
         i = 0
         while i < len(self.order):
             run = (self.fused_runs if ctx.decode else self.prompt_runs).get(i)
@@ -124,6 +133,12 @@ class CausalLM:
                 ctx.settle(residual)
             blk.forward(residual, ctx, cache.view(i), cache.state.view(i), self.positions)
             i += 1
+        if streams is not None:
+            ctx.settle_streams(residual)       # the last sublayer's write
+            if want_rows is None or want_rows.numel() == 0:
+                return None
+            # the streams' sum through the final norm, wanted rows only
+            return self.head.forward(self.final_norm.forward_streams(residual, None, want_rows))
         if want_rows is None or want_rows.numel() == 0:
             ctx.settle(residual)
             return None

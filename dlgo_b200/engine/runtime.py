@@ -83,6 +83,7 @@ class StepContext:
     capacity: int = 0            # longest sequence the cache can hold
     want_identity: bool = False  # the wanted rows are exactly rows 0..T-1, each once
     pending: Optional[torch.Tensor] = None   # fp32 [slices, T, d] still to be added to the residual stream
+    owed: Optional[dict] = None              # a write into several residual streams that the next reader performs
     _tiles: Dict[Tuple[int, bool], Tuple[torch.Tensor, int, int]] = field(default_factory=dict)
     _scratch: Dict[str, torch.Tensor] = field(default_factory=dict)
 
@@ -138,6 +139,24 @@ class StepContext:
         if p is not None:
             from ..csrc import kernels as K
             K.add_rmsnorm(residual, p, None, 0.0, None)
+
+    # On several residual streams a sublayer's result returns through a write (kernels.streams_step) that
+    # whoever reads the streams next performs in the same launch as its own read.
+    def owe_write(self, streams: torch.Tensor, write: dict) -> None:
+        if self.owed is not None:
+            self.settle_streams(streams)
+        self.owed = write
+
+    def take_owed_write(self) -> Optional[dict]:
+        w, self.owed = self.owed, None
+        return w
+
+    def settle_streams(self, streams: torch.Tensor) -> None:
+        """Perform the owed write now."""
+        w = self.take_owed_write()
+        if w is not None:
+            from ..csrc import kernels as K
+            K.streams_step(streams, **w)
 
     def zeros(self, name: str, numel: int, dtype: torch.dtype = torch.int32) -> torch.Tensor:
         """A buffer that is zero when first handed out; kernels that use it leave it zero."""

@@ -32,7 +32,8 @@ class ParamSpec:
     """One tensor a part wants from the weight file.
 
     ``init`` says how the random-weights mode fills it: ``"normal"`` is
-    N(0, std), ``"one_plus_normal"`` is 1 + N(0, std) (norm weights).
+    N(0, std), ``"one_plus_normal"`` is 1 + N(0, std) (norm weights),
+    ``"identity_plus_normal"`` is I + N(0, std) for a square matrix.
     """
 
     shape: Tuple[int, ...]
@@ -46,13 +47,15 @@ class CacheNeed:
     Entries of the run order whose needs are equal and that name the same
     ``group`` share one allocation.  ``window`` (positions) is ``None`` for
     "all keys"; a windowed group gives pages back once every position in them
-    lies outside the window of all queries still to come.
+    lies outside the window of all queries still to come.  ``planes``: 2 keeps
+    keys and values; 1 keeps one row per position that serves as both (a latent).
     """
 
     group: str
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    planes: int = 2
 
 
 @dataclass(frozen=True)
@@ -119,14 +122,17 @@ class Block:
     ``forward`` decides who reads the residual stream when.
     """
 
-    def __init__(self, mixer: Optional[Mixer], ffn: Optional[FeedForward], norms: Mapping[str, Norm]):
+    def __init__(self, mixer: Optional[Mixer], ffn: Optional[FeedForward], norms: Mapping[str, Norm],
+                 connections: Optional[Mapping[str, Part]] = None):
         self.mixer = mixer
         self.ffn = ffn
         self.norms: Dict[str, Norm] = dict(norms)
+        self.connections: Dict[str, Part] = dict(connections or {})
 
     def parts(self) -> Dict[str, Part]:
-        """Every part of the layer by role (norm roles, ``mixer``, ``ffn``): what holds its tensors."""
+        """Every part of the layer by role (norm and connection roles, ``mixer``, ``ffn``): what holds its tensors."""
         out: Dict[str, Part] = dict(self.norms)
+        out.update(self.connections)
         if self.mixer is not None:
             out["mixer"] = self.mixer
         if self.ffn is not None:

@@ -10,8 +10,9 @@ from typing import Any, Mapping, Optional
 
 import torch
 
-from .base import Block, PositionEncoding
-from .registry import BLOCKS
+from ..csrc import kernels as K
+from .base import Block, ParamSpec, Part, PositionEncoding
+from .registry import BLOCKS, CONNECTIONS
 
 
 def norm_of(norm: Any, residual: torch.Tensor, ctx: Any) -> torch.Tensor:
@@ -29,8 +30,8 @@ def norm_of(norm: Any, residual: torch.Tensor, ctx: Any) -> torch.Tensor:
 class PreNormBlock(Block):
     handles_pending = True   # reads the residual only through norm_of
 
-    def __init__(self, mixer: Any, ffn: Any, norms: Mapping[str, Any]):
-        super().__init__(mixer, ffn, norms)
+    def __init__(self, mixer: Any, ffn: Any, norms: Mapping[str, Any], connections: Any = None):
+        super().__init__(mixer, ffn, norms, connections)
         missing = [r for r in ("mixer_norm", "ffn_norm") if r not in self.norms]
         if missing or mixer is None or ffn is None:
             raise ValueError("a pre-norm block needs a mixer, a feed-forward and the norms 'mixer_norm' and 'ffn_norm'"
@@ -46,4 +47,87 @@ class PreNormBlock(Block):
         self.ffn.forward(x, residual, ctx)
 
 
+class HyperConnection(Part):
+    """How one sublayer sits on ``streams`` residual streams x_1 .. x_s: it reads ``u = sum_r read[r] x_r`` and
+    its result y returns as ``x_q <- sum_r mix[r, q] x_r + write[q] * y`` for every q at once (``mix`` is
+    indexed [from, to]).  With one stream, read = write = mix = 1 this is the plain residual sum.
+    ``names``: tensor names of the three below the part's prefix."""
+
+    def __init__(self, streams: int, names: Optional[Mapping[str, str]] = None):
+        super().__init__(streams=streams, names=names)
+        if not 1 <= int(streams) <= K.MAX_STREAMS:
+            raise ValueError(f"streams must be 1 to {K.MAX_STREAMS}, got {streams}")
+        self.streams = int(streams)
+        self.names = {"read": "read", "write": "write", "mix": "mix"}
+        self.names.update(names or {})
+        self.read: Optional[torch.Tensor] = None
+        self.write: Optional[torch.Tensor] = None
+        self.mix: Optional[torch.Tensor] = None
+
+    def param_specs(self):
+        s = self.streams
+        return {self.names["read"]: ParamSpec((s,), "one_plus_normal"),
+                self.names["write"]: ParamSpec((s,), "one_plus_normal"),
+                self.names["mix"]: ParamSpec((s, s), "identity_plus_normal")}
+
+    def load(self, get: Any, runtime: Any) -> None:
+        # coefficients of the residual sum: fp32 in every precision
+        self.read = get(self.names["read"]).to(torch.float32).contiguous()
+        self.write = get(self.names["write"]).to(torch.float32).contiguous()
+        self.mix = get(self.names["mix"]).to(torch.float32).contiguous()
+
+
+class HyperPreNormBlock(Block):
+    """Pre-norm layer on several residual streams [tokens, streams, hidden] (fp32): every sublayer that is
+    there (``mixer``, then ``ffn``) reads the streams through its connection and its norm and writes back
+    through the connection.  A sublayer adds its result into a zeroed [tokens, hidden] buffer, as it would
+    into a single residual stream; the write reads that buffer and leaves it zero for the next sublayer.
+    The write of one sublayer and the read and norm of the next are one launch (also across layers: the
+    last write of a layer is left for the next layer's first read, or for whoever reads the streams next)."""
+
+    handles_pending = False
+    on_streams = True
+
+    def __init__(self, mixer: Any, ffn: Any, norms: Mapping[str, Any], connections: Any = None):
+        super().__init__(mixer, ffn, norms, connections)
+        self.sublayers = []
+        for part, norm, conn in ((mixer, "mixer_norm", "mixer_conn"), (ffn, "ffn_norm", "ffn_conn")):
+            if part is None:
+                continue
+            if norm not in self.norms or conn not in self.connections:
+                raise ValueError(f"a block on residual streams needs the norm {norm!r} and the connection {conn!r}")
+            if not hasattr(self.norms[norm], "step_args"):
+                raise ValueError(f"the norm {norm!r} cannot read residual streams")
+            self.sublayers.append((part, self.norms[norm], self.connections[conn]))
+        if mixer is None:
+            raise ValueError("a block needs a mixer")
+
+    def forward(self, streams: torch.Tensor, ctx: Any, cache: Any, state: Optional[torch.Tensor],
+                positions: Mapping[str, PositionEncoding]) -> None:
+        T, s, d = streams.shape
+        y = ctx.zeros(f"sublayer_out{d}", T * d, torch.float32)[:T * d].view(T, d)
+        for part, norm, conn in self.sublayers:
+            owed = ctx.take_owed_write() if hasattr(ctx, "take_owed_write") else None
+            if owed is not None:
+                x = K.streams_step(streams, read=conn.read, **owed, **norm.step_args())
+            else:
+                x = norm.forward_streams(streams, conn.read)
+            bias = None
+            if part is self.mixer:
+                part.forward(x, y, ctx, cache, state, positions)
+            elif getattr(part, "can_defer_bias", False):
+                part.forward(x, y, ctx, defer_bias=True)      # the write adds the output bias in its own pass
+                bias = part.output_bias
+            else:
+                part.forward(x, y, ctx)
+            ctx.settle(y)
+            write = dict(y=y, y_bias=bias, mix=conn.mix, write=conn.write, clear_y=True)
+            if hasattr(ctx, "owe_write"):
+                ctx.owe_write(streams, write)
+            else:
+                K.streams_step(streams, **write)
+
+
 BLOCKS.register("prenorm", PreNormBlock)
+BLOCKS.register("hyper_prenorm", HyperPreNormBlock)
+CONNECTIONS.register("hyper_connection", HyperConnection)

@@ -18,37 +18,42 @@ from .registry import EMBEDDINGS, HEADS
 
 
 class TokenEmbedding(Part):
-    def __init__(self, vocab_size: int, hidden_size: int):
-        super().__init__(vocab_size=vocab_size, hidden_size=hidden_size)
+    """``name``: the table's tensor name below the part's prefix."""
+
+    def __init__(self, vocab_size: int, hidden_size: int, name: str = "weight"):
+        super().__init__(vocab_size=vocab_size, hidden_size=hidden_size, name=name)
         self.vocab_size = int(vocab_size)
         self.hidden_size = int(hidden_size)
+        self.name = name
         self.table: Optional[torch.Tensor] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {"weight": ParamSpec((self.vocab_size, self.hidden_size))}
+        return {self.name: ParamSpec((self.vocab_size, self.hidden_size))}
 
     def load(self, get: Callable[[str], torch.Tensor], runtime: Any) -> None:
-        self.table = runtime.compute_copy(get("weight")).contiguous()
+        self.table = runtime.compute_copy(get(self.name)).contiguous()
 
-    def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
-        return K.embed(token_ids, self.table)
+    def forward(self, token_ids: torch.Tensor, copies: Optional[int] = None) -> torch.Tensor:
+        """fp32 rows [T, hidden]; with ``copies`` = s, [T, s, hidden] with every copy equal (residual streams)."""
+        return K.embed(token_ids, self.table, copies=copies)
 
 
 class LinearHead(Part):
     """``tied_to`` names the tensor (absolute name) the head shares, or ``None`` for a weight of its own."""
 
-    def __init__(self, vocab_size: int, hidden_size: int, tied_to: Optional[str] = None):
-        super().__init__(vocab_size=vocab_size, hidden_size=hidden_size, tied_to=tied_to)
+    def __init__(self, vocab_size: int, hidden_size: int, tied_to: Optional[str] = None, name: str = "weight"):
+        super().__init__(vocab_size=vocab_size, hidden_size=hidden_size, tied_to=tied_to, name=name)
         self.vocab_size = int(vocab_size)
         self.hidden_size = int(hidden_size)
         self.tied_to = tied_to
+        self.name = name
         self.proj: Optional[Linear] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {} if self.tied_to else {"weight": ParamSpec((self.vocab_size, self.hidden_size))}
+        return {} if self.tied_to else {self.name: ParamSpec((self.vocab_size, self.hidden_size))}
 
     def load(self, get: Callable[[str], torch.Tensor], runtime: Any) -> None:
-        self.proj = Linear(get("weight"), runtime)
+        self.proj = Linear(get(self.name), runtime)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return self.proj(x, STORE_F32)

@@ -7,13 +7,13 @@ experts, no routing.
 """
 from __future__ import annotations
 
-from typing import Any, Callable, Dict, Optional
+from typing import Any, Callable, Dict, Mapping, Optional
 
 import torch
 
 from ..csrc import kernels as K
 from .base import FeedForward, ParamSpec
-from .linear import ADD_F32, STORE, Linear
+from .linear import ADD_F32, STORE, STORE_F32, Linear
 from .registry import FEED_FORWARDS
 
 
@@ -59,4 +59,50 @@ class SwiGLU(FeedForward):
             self.w_down(h, ADD_F32, residual)
 
 
+class ReluSquaredMLP(FeedForward):
+    """Dense two-matrix feed-forward with the square of relu between: ``y = Wd . relu(Wu . x + bu)^2 + bd``
+    (``bias`` False: no bu, bd).  ``names``: tensor names below the part's prefix.  Bias and activation run in
+    fp32 on the contraction's fp32 result."""
+
+    can_defer_bias = True
+
+    def __init__(self, hidden_size: int, intermediate_size: int, bias: bool = False,
+                 names: Optional[Mapping[str, str]] = None):
+        super().__init__(hidden_size=hidden_size, intermediate_size=intermediate_size, bias=bias, names=names)
+        self.hidden_size = int(hidden_size)
+        self.intermediate_size = int(intermediate_size)
+        self.bias = bool(bias)
+        self.names = {"up": "up_proj.weight", "up_bias": "up_proj.bias", "down": "down_proj.weight",
+                      "down_bias": "down_proj.bias"}
+        self.names.update(names or {})
+        self.w_up: Optional[Linear] = None
+        self.w_down: Optional[Linear] = None
+        self.b_up: Optional[torch.Tensor] = None
+        self.output_bias: Optional[torch.Tensor] = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        n, f, d = self.names, self.intermediate_size, self.hidden_size
+        specs = {n["up"]: ParamSpec((f, d)), n["down"]: ParamSpec((d, f))}
+        if self.bias:
+            specs[n["up_bias"]] = ParamSpec((f,))
+            specs[n["down_bias"]] = ParamSpec((d,))
+        return specs
+
+    def load(self, get: Callable[[str], torch.Tensor], runtime: Any) -> None:
+        n = self.names
+        self.w_up = Linear(get(n["up"]), runtime)
+        self.w_down = Linear(get(n["down"]), runtime)
+        if self.bias:
+            self.b_up = get(n["up_bias"]).to(torch.float32).contiguous()
+            self.output_bias = get(n["down_bias"]).to(torch.float32).contiguous()
+
+    def forward(self, x: Any, residual: torch.Tensor, ctx: Any, defer_bias: bool = False) -> None:
+        """``defer_bias``: the caller adds :attr:`output_bias` itself (fused into its next pass over the result)."""
+        h = K.bias_act(self.w_up(x, STORE_F32), self.b_up, K.ACT_RELU2, self.w_down.weight.dtype)
+        if self.output_bias is not None and not defer_bias:
+            K.bias_act(residual, self.output_bias, K.ACT_NONE, torch.float32, in_place=True)
+        self.w_down(h, ADD_F32, residual)
+
+
 FEED_FORWARDS.register("swiglu", SwiGLU)
+FEED_FORWARDS.register("relu2_mlp", ReluSquaredMLP)

@@ -1,0 +1,116 @@
+"""Attention over a cache of latents, without positions.
+
+Every position keeps ONE vector for all heads: ``c = rms(Wd h) * g`` of ``kv_rank`` numbers.  A head's keys
+and values are linear in it (``k = Wk c``, ``v = Wv c``), so the cache holds only ``c`` and the kernel never
+builds keys or values: ``score = (Wk^T q) . c * scale`` and ``out = Wv (sum_j p_j c_j)``.
+
+Options, all constants of the part:
+
+* ``q_rank``: the queries go through a latent of their own, ``q = Wu rms(Wq h) * gq``; ``None``: ``q = Wq h``
+* ``window``: position i sees j with ``0 <= i - j < window``; ``None``: every j <= i
+* ``sink``: a learned number per head joins the softmax's denominator as ``exp(sink)`` (no key, no value,
+  not scaled)
+
+The down-projections of queries and latents are one contraction with an fp32 result, because their RMS
+norms are taken in fp32; scores, softmax and the weighted sum are fp32 in every precision.
+"""
+from __future__ import annotations
+
+from typing import Any, Callable, Dict, Mapping, Optional
+
+import torch
+
+from ..csrc import kernels as K
+from .base import CacheNeed, Mixer, ParamSpec, PositionEncoding
+from .linear import ADD_F32, STORE, STORE_F32, Linear
+from .registry import MIXERS
+
+_NAMES = {"q": "q_proj.weight", "q_down": "q_a_proj.weight", "q_norm": "q_a_norm.weight", "q_up": "q_b_proj.weight",
+          "kv_down": "kv_a_proj.weight", "kv_norm": "kv_a_norm.weight", "k_up": "k_b_proj.weight",
+          "v_up": "v_b_proj.weight", "sink": "sinks", "out": "o_proj.weight"}
+
+
+class LatentAttention(Mixer):
+    def __init__(self, hidden_size: int, num_heads: int, qk_dim: int, v_dim: int, kv_rank: int, scale: float,
+                 eps: float, q_rank: Optional[int] = None, window: Optional[int] = None, sink: bool = False,
+                 cache_group: str = "latent", names: Optional[Mapping[str, str]] = None):
+        super().__init__(hidden_size=hidden_size, num_heads=num_heads, qk_dim=qk_dim, v_dim=v_dim, kv_rank=kv_rank,
+                         scale=scale, eps=eps, q_rank=q_rank, window=window, sink=sink, cache_group=cache_group,
+                         names=names)
+        if kv_rank % 2 or kv_rank > 1024:
+            raise ValueError(f"kv_rank must be even and at most 1024, got {kv_rank}")
+        if window is not None and window <= 0:
+            raise ValueError(f"window must be positive or None, got {window}")
+        self.hidden_size, self.n_heads = int(hidden_size), int(num_heads)
+        self.qk_dim, self.v_dim, self.kv_rank = int(qk_dim), int(v_dim), int(kv_rank)
+        self.q_rank = None if q_rank is None else int(q_rank)
+        self.scale, self.eps = float(scale), float(eps)
+        self.window = None if window is None else int(window)
+        self.has_sink = bool(sink)
+        self.cache_group = cache_group
+        self.names = dict(_NAMES)
+        self.names.update(names or {})
+        self.w_down: Optional[Linear] = None      # rows: query part (q_down or q) | kv_down
+        self.w_q_up: Optional[Linear] = None
+        self.w_k_up: Optional[torch.Tensor] = None
+        self.w_v_up: Optional[torch.Tensor] = None
+        self.wo: Optional[Linear] = None
+        self.q_norm: Optional[torch.Tensor] = None
+        self.kv_norm: Optional[torch.Tensor] = None
+        self.sink: Optional[torch.Tensor] = None
+
+    # --------------------------------------------------------------- declarations
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        n, d, H = self.names, self.hidden_size, self.n_heads
+        specs = {
+            n["kv_down"]: ParamSpec((self.kv_rank, d)),
+            n["kv_norm"]: ParamSpec((self.kv_rank,), "one_plus_normal"),
+            n["k_up"]: ParamSpec((H * self.qk_dim, self.kv_rank)),
+            n["v_up"]: ParamSpec((H * self.v_dim, self.kv_rank)),
+            n["out"]: ParamSpec((d, H * self.v_dim)),
+        }
+        if self.q_rank is not None:
+            specs[n["q_down"]] = ParamSpec((self.q_rank, d))
+            specs[n["q_norm"]] = ParamSpec((self.q_rank,), "one_plus_normal")
+            specs[n["q_up"]] = ParamSpec((H * self.qk_dim, self.q_rank))
+        else:
+            specs[n["q"]] = ParamSpec((H * self.qk_dim, d))
+        if self.has_sink:
+            specs[n["sink"]] = ParamSpec((H,))
+        return specs
+
+    def cache_need(self) -> CacheNeed:
+        # one "kv head" whose rows are the latents; keys and values are the same plane
+        return CacheNeed(self.cache_group, 1, self.kv_rank, self.window, planes=1)
+
+    def load(self, get: Callable[[str], torch.Tensor], runtime: Any) -> None:
+        n = self.names
+        first = get(n["q_down"] if self.q_rank is not None else n["q"])
+        self.w_down = Linear(torch.cat([runtime.compute_copy(first), runtime.compute_copy(get(n["kv_down"]))], dim=0),
+                             runtime)
+        self.kv_norm = get(n["kv_norm"]).to(torch.float32).contiguous()
+        if self.q_rank is not None:
+            self.q_norm = get(n["q_norm"]).to(torch.float32).contiguous()
+            self.w_q_up = Linear(get(n["q_up"]), runtime)
+        self.w_k_up = runtime.compute_copy(get(n["k_up"])).contiguous()
+        self.w_v_up = runtime.compute_copy(get(n["v_up"])).contiguous()
+        if self.has_sink:
+            self.sink = get(n["sink"]).to(torch.float32).contiguous()
+        self.wo = Linear(get(n["out"]), runtime)
+
+    # -------------------------------------------------------------------- forward
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: Any, cache: Any,
+                state: Optional[torch.Tensor], positions: Mapping[str, PositionEncoding]) -> None:
+        n_q = self.q_rank if self.q_rank is not None else self.n_heads * self.qk_dim
+        proj = self.w_down(x, STORE_F32)                       # [T, n_q + kv_rank] fp32
+        cq = K.latent_norm_append(proj, n_q, self.kv_rank, self.kv_norm, 0, self.q_rank or 0, self.q_norm, self.eps,
+                                  ctx.token_pos, ctx.token_seq, ctx.seq_slot, cache.page_table, cache.keys,
+                                  cache.writes)
+        q = self.w_q_up(cq, STORE) if self.q_rank is not None else proj[:, :n_q]
+        out = K.latent_attention(q, self.w_k_up, self.w_v_up, self.sink, cache.keys, cache.page_table, ctx.seq_slot,
+                                 ctx.token_seq, ctx.token_pos, self.n_heads, self.qk_dim, self.v_dim, self.scale,
+                                 self.window or 0)
+        self.wo(out, ADD_F32, residual)
+
+
+MIXERS.register("latent_attention", LatentAttention)

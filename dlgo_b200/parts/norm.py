@@ -35,4 +35,61 @@ class RMSNorm(Norm):
         return K.add_rmsnorm(residual, parts, self.weight, self.eps, self.out_dtype, rows)
 
 
+class DynamicTanh(Norm):
+    """Dynamic Tanh: ``out = tanh(alpha * x) * w + b`` element by element, with a learned scalar ``alpha``;
+    no mean, no variance, no eps.  ``names`` gives the tensor names of weight, bias and alpha below the
+    part's prefix."""
+
+    kind = K.NORM_DYT
+
+    def __init__(self, size: int, names: Optional[Dict[str, str]] = None):
+        super().__init__(size=size, names=names)
+        self.size = int(size)
+        self.names = {"weight": "weight", "bias": "bias", "alpha": "alpha"}
+        self.names.update(names or {})
+        self.eps = 0.0
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+        self.alpha: Optional[torch.Tensor] = None
+        self.out_dtype: Optional[torch.dtype] = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {self.names["weight"]: ParamSpec((self.size,), "one_plus_normal"),
+                self.names["bias"]: ParamSpec((self.size,)),
+                self.names["alpha"]: ParamSpec((), "one_plus_normal")}
+
+    def load(self, get: Callable[[str], torch.Tensor], runtime: Any) -> None:
+        self.weight = get(self.names["weight"]).to(torch.float32).contiguous()
+        self.bias = get(self.names["bias"]).to(torch.float32).contiguous()
+        self.alpha = get(self.names["alpha"]).to(torch.float32).reshape(1).contiguous()
+        self.out_dtype = runtime.dtype
+
+    def forward(self, residual: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return self.forward_streams(residual.view(residual.shape[0], 1, -1), None, rows)
+
+    def forward_streams(self, streams: torch.Tensor, read: Optional[torch.Tensor] = None,
+                        rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The norm of ``sum_r read[r] * streams[:, r]`` (``read`` None: the plain sum) for streams [T, s, d]."""
+        return K.streams_step(streams, read=read, norm_kind=K.NORM_DYT, norm_w=self.weight, norm_b=self.bias,
+                              norm_alpha=self.alpha, out_dtype=self.out_dtype, rows=rows)
+
+    def step_args(self) -> Dict[str, Any]:
+        """This norm as arguments of :func:`kernels.streams_step` (for a caller that fuses it with a write)."""
+        return dict(norm_kind=K.NORM_DYT, norm_w=self.weight, norm_b=self.bias, norm_alpha=self.alpha,
+                    out_dtype=self.out_dtype)
+
+
+def _rms_forward_streams(self, streams: torch.Tensor, read: Optional[torch.Tensor] = None,
+                         rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    return K.streams_step(streams, read=read, rows=rows, **self.step_args())
+
+
+def _rms_step_args(self) -> Dict[str, Any]:
+    return dict(norm_kind=K.NORM_RMS, norm_w=self.weight, eps=self.eps, out_dtype=self.out_dtype)
+
+
+RMSNorm.forward_streams = _rms_forward_streams
+RMSNorm.step_args = _rms_step_args
+
 NORMS.register("rmsnorm", RMSNorm)
+NORMS.register("dynamic_tanh", DynamicTanh)

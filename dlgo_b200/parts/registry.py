@@ -42,6 +42,7 @@ POSITION_ENCODINGS = PartRegistry("position encoding")
 BLOCKS = PartRegistry("block")
 EMBEDDINGS = PartRegistry("embedding")
 HEADS = PartRegistry("head")
+CONNECTIONS = PartRegistry("connection")
 
 
 def register_mixer(kind: str, factory: Callable[..., Any], **kw: Any) -> None:
@@ -58,6 +59,10 @@ def register_norm(kind: str, factory: Callable[..., Any], **kw: Any) -> None:
 
 def register_position_encoding(kind: str, factory: Callable[..., Any], **kw: Any) -> None:
     POSITION_ENCODINGS.register(kind, factory, **kw)
+
+
+def register_connection(kind: str, factory: Callable[..., Any], **kw: Any) -> None:
+    CONNECTIONS.register(kind, factory, **kw)
 
 
 def register_block(kind: str, factory: Callable[..., Any], **kw: Any) -> None:
