@@ -320,6 +320,131 @@ def phase_stamps(llm, batch):
     return 0
 
 
+# --only dedutar: the Dedutar design beside Llama at equal layer sizes (random weights)
+DEDUTAR_SIZES = {
+    # width, feed-forward, heads, head size, latent rank, query rank, window, layers run
+    "1b": dict(width=2048, ff=8192, heads=16, dim=128, kv_rank=512, q_rank=768, window=1024, vocab=32000),
+    "3b": dict(width=3072, ff=8192, heads=24, dim=128, kv_rank=512, q_rank=1536, window=1024, vocab=32000),
+    "small": dict(width=1024, ff=4096, heads=16, dim=64, kv_rank=256, q_rank=384, window=512, vocab=32000),
+}
+
+
+def dedutar_pair(size):
+    """(Dedutar config.json, Llama config.json): four layers (linear attention, windowed latent attention,
+    latent attention with a sink twice), each with a feed-forward, run twice; Llama with as many layers of the
+    same width, feed-forward, heads and head size."""
+    z = DEDUTAR_SIZES[size]
+    H, hd = z["heads"], z["dim"]
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    lat2 = {"type": "latent_attention_2", "mlp": mlp,
+            "mixer": {"heads": H, "dim": hd, "vdim": hd, "kv_rank": z["kv_rank"], "scale": hd ** -0.5}}
+    ded = {"architecture": "Dedutar", "vocab": z["vocab"], "width": z["width"], "streams": 2, "norm": {"eps": 1e-6},
+           "loop": {"start": 0, "stop": 4, "times": 2},
+           "layers": [
+               {"type": "lightning", "mlp": mlp,
+                "mixer": {"heads": H, "dim": hd, "vdim": hd, "decay": [1.0 - 2.0 ** -(3 + 5 * i / H) for i in range(H)]}},
+               {"type": "latent_attention", "mlp": mlp,
+                "mixer": {"heads": H, "dim": hd, "vdim": hd, "kv_rank": z["kv_rank"], "q_rank": z["q_rank"],
+                          "scale": hd ** -0.5, "mask": {"size": z["window"]}}},
+               lat2, lat2]}
+    llama = dict(architectures=["LlamaForCausalLM"], hidden_size=z["width"], num_hidden_layers=8,
+                 intermediate_size=z["ff"], num_attention_heads=H, num_key_value_heads=max(1, H // 4), head_dim=hd,
+                 vocab_size=z["vocab"], rope_theta=500000.0, rope_scaling=None, rms_norm_eps=1e-5,
+                 max_position_embeddings=8192, tie_word_embeddings=False)
+    return ded, llama
+
+
+def dedutar_compare(size, batch, steps, warmup, prefill_tokens, profile):
+    """Prefill and decode throughput of both models, and (with `profile`) the time per kernel entry point of
+    one prompt step and of decode steps launched one by one."""
+    import torch
+    import dlgo_b200
+    from dlgo_b200.config import config_from_dict
+    from dlgo_b200.csrc import kernels
+    from dlgo_b200.weights import write_random_model
+    out = {"only": "dedutar", "size": size, "batch": batch, "prefill_tokens": prefill_tokens, "dtype": "bf16",
+           "data": "synthetic", "models": {}}
+    for name, cfg in zip(("dedutar", "llama"), dedutar_pair(size)):
+        tmp = tempfile.mkdtemp(prefix=f"bench_{name}_")
+        try:
+            write_random_model(config_from_dict(cfg), 2, tmp, device="cuda")
+            llm = dlgo_b200.load_llm(tmp, dtype="bfloat16", max_tokens=batch * 2048 + prefill_tokens + 1024,
+                                     cuda_graphs=True)
+        finally:
+            shutil.rmtree(tmp, ignore_errors=True)
+        eng = llm.engine
+        V = cfg.get("vocab", cfg.get("vocab_size"))
+        g = torch.Generator().manual_seed(5)
+
+        def prompt_step(n, reps=5):
+            times = []
+            for r in range(reps + 2):
+                toks = torch.randint(0, V, (n,), generator=g).tolist()
+                s = eng.take_slot()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                a.record()
+                eng.step([s], [toks])
+                b.record()
+                torch.cuda.synchronize()
+                eng.free_slot(s)
+                if r >= 2:
+                    times.append(a.elapsed_time(b))
+            return statistics.median(times) if times else 0.0
+
+        def decode_steps(n_steps, n_warm, context=512):
+            slots = [eng.take_slot() for _ in range(batch)]
+            eng.step(slots, [torch.randint(0, V, (context,), generator=g).tolist() for _ in slots])
+            feed = [[int(t)] for t in torch.randint(0, V, (batch,), generator=g)]
+            for _ in range(n_warm):
+                eng.step(slots, feed)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            for _ in range(n_steps):
+                eng.step(slots, feed)
+            b.record()
+            torch.cuda.synchronize()
+            for s in slots:
+                eng.free_slot(s)
+            return a.elapsed_time(b) / n_steps
+
+        ms_p = prompt_step(prefill_tokens)
+        ms_d = decode_steps(steps, warmup)
+        res = {"prefill_ms": round(ms_p, 3), "prefill_tok_s": round(prefill_tokens / (ms_p / 1e3), 1),
+               "decode_ms_per_step": round(ms_d, 4), "decode_tok_s": round(batch / (ms_d / 1e3), 1),
+               "weight_gb": round(eng.weight_bytes() / 1e9, 3)}
+        if profile:
+            os.environ["DLGO_NATIVE_PROMPT"] = "0"
+            eng.cuda_graphs = False
+            for what, fn in (("prefill_kernels", lambda: prompt_step(prefill_tokens, reps=0)),
+                             ("decode_kernels", lambda: decode_steps(4, 2))):
+                fn()
+                kernels.profile_start()
+                s = eng.take_slot() if what == "prefill_kernels" else None
+                if what == "prefill_kernels":
+                    eng.model.prompt_runs = {}
+                    eng.step([s], [torch.randint(0, V, (prefill_tokens,), generator=g).tolist()])
+                    eng.free_slot(s)
+                    n = 1
+                else:
+                    slots = [eng.take_slot() for _ in range(batch)]
+                    eng.step(slots, [torch.randint(0, V, (512,), generator=g).tolist() for _ in slots])
+                    kernels.profile_stop()
+                    kernels.profile_start()
+                    feed = [[1]] * batch
+                    for _ in range(4):
+                        eng.step(slots, feed)
+                    for sl in slots:
+                        eng.free_slot(sl)
+                    n = 4
+                res[what] = {k: [c // n, round(ms / n, 4)] for k, c, ms in kernels.profile_stop()}
+        out["models"][name] = res
+        del llm, eng
+        torch.cuda.empty_cache()
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -335,8 +460,11 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="--only prefill: tokens of the prompt")
     ap.add_argument("--prefill-batch", type=int, default=0,
                     help="--only prefill: a packed batch of that many prompts with lengths from --prompt-range")
-    ap.add_argument("--only", choices=["decode", "prefill", "phases", "sampled"],
-                    help="run one small workload (for profiling) and stop; phases: see phase_stamps()")
+    ap.add_argument("--only", choices=["decode", "prefill", "phases", "sampled", "dedutar"],
+                    help="run one small workload (for profiling) and stop; phases: see phase_stamps(); dedutar: "
+                         "prefill and decode of the Dedutar design beside Llama at equal layer sizes")
+    ap.add_argument("--dedutar-size", default="1b", choices=sorted(DEDUTAR_SIZES), help="--only dedutar: layer sizes")
+    ap.add_argument("--kernels", action="store_true", help="--only dedutar: also the time per kernel entry point")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode kernels one by one (for profiling)")
     a = ap.parse_args()
     if a.impl == "reference":
@@ -353,6 +481,9 @@ def main() -> int:
     import torch
     import dlgo_b200
     warmup = max(a.warmup, 3)
+    if a.only == "dedutar":
+        print(json.dumps(dedutar_compare(a.dedutar_size, a.batch, a.steps, warmup, a.prefill_tokens, a.kernels)))
+        return 0
     pk = peaks()
     global PROMPT_LEN, PROMPT_RANGE
     PROMPT_LEN = a.prompt_len

@@ -46,6 +46,9 @@ struct PfParams {
   int ldo;
   int Hq, Hkv, window;
   float scale_log2e;      // score scale times log2(e)
+  const float* sink;      // [Hq] or null: exp(sink) joins a row's denominator (no key, no value, not scaled)
+  int kv_rows;            // 0: keys and values lie in the cache's layout [page][kv head][64][HD];
+                          // 1: as rows of tokens [page * 64 + key][kv head * HD ...] (keys and values made for the step)
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -86,8 +89,12 @@ __device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint3
   return d;
 }
 
-template <int HD>
-__global__ void __launch_bounds__(PF_THREADS, HD <= 64 ? 3 : 2)
+// SPLIT: a probability enters P V as the sum of two bfloat16 numbers (its rounding and the rounding of what
+// that left over), each in a P tile of its own and both multiplied with the same values: the weights then
+// carry 16 bits of mantissa into the product instead of 8, for models whose softmax weights are to stay
+// 32-bit quantities.
+template <int HD, bool SPLIT>
+__global__ void __launch_bounds__(PF_THREADS, (HD <= 64 && !SPLIT) ? 3 : 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, PfParams p) {
   constexpr int NCH = HD / 64;                 // 64-wide chunks of the head
@@ -107,7 +114,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   uint8_t* k_s = q_s + QBYTES;                 // 2 stages
   uint8_t* v_s = k_s + 2 * KVBYTES;            // 2 stages
   uint8_t* p_s = v_s + 2 * KVBYTES;
-  uint64_t* bars = (uint64_t*)(p_s + PBYTES);
+  uint8_t* p2_s = p_s + PBYTES;                // (SPLIT) what the first tile's rounding left over
+  uint64_t* bars = (uint64_t*)(p_s + (SPLIT ? 2 : 1) * PBYTES);
   uint64_t* qfull = bars;          // 1
   uint64_t* kfull = bars + 1;      // 2
   uint64_t* vfull = bars + 3;      // 2
@@ -171,6 +179,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       for (int j = 0; j < NCH; ++j) tma_load_2d(q_s + j * 16384, &map_q, qfull, head * HD + j * 64, tok0);
       // keys run one block ahead of values: a stage's keys are free once their scores have completed,
       // its values only after the P V that follows a whole softmax later
+      const int kv_col = p.kv_rows ? kvh * HD : 0;
       auto page_of = [&](int it) {
         const int pg = kb_first + it;
         return (pg >= first_live_page && pg <= last_page) ? p.page_table[(size_t)slot * p.max_pages + pg] : -1;
@@ -182,7 +191,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         mbar_expect_tx(&kfull[st], page >= 0 ? NCH * 8192 : 0);
         if (page >= 0)
           for (int j = 0; j < NCH; ++j)
-            tma_load_2d(k_s + st * KVBYTES + j * 8192, &map_k, &kfull[st], j * 64, (page * p.Hkv + kvh) * 64);
+            tma_load_2d(k_s + st * KVBYTES + j * 8192, &map_k, &kfull[st], kv_col + j * 64,
+                        p.kv_rows ? page * 64 : (page * p.Hkv + kvh) * 64);
         return true;
       };
       auto load_v = [&](int it) {
@@ -192,7 +202,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         mbar_expect_tx(&vfull[st], page >= 0 ? NCH * 8192 : 0);
         if (page >= 0)
           for (int j = 0; j < NCH; ++j)
-            tma_load_2d(v_s + st * KVBYTES + j * 8192, &map_v, &vfull[st], j * 64, (page * p.Hkv + kvh) * 64);
+            tma_load_2d(v_s + st * KVBYTES + j * 8192, &map_v, &vfull[st], kv_col + j * 64,
+                        p.kv_rows ? page * 64 : (page * p.Hkv + kvh) * 64);
         return true;
       };
       bool ok = load_k(0);
@@ -205,7 +216,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (elect_one()) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(PF_ROWS, PF_KEYS);
       constexpr uint32_t idesc_o = umma_idesc_bf16(PF_ROWS, HD) | (1u << 16);   // B is MN-major
-      const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
+      const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s), p2_addr = smem_u32(p2_s);
       bool ok = mbar_wait(qfull, 0, abort_flag) && mbar_wait(&kfull[0], 0, abort_flag);
       if (ok) {
         tc_fence_after_sync();
@@ -246,6 +257,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int kk = 0; kk < PF_KEYS / 16; ++kk)
           umma_bf16(tmem_base + O_COL, umma_desc_k_sw128(p_addr) + 2 * kk,
                     umma_desc_mn_sw128(v_addr + kk * 2048, 8192), idesc_o, (it | kk) != 0);
+        if (SPLIT) {
+#pragma unroll
+          for (int kk = 0; kk < PF_KEYS / 16; ++kk)
+            umma_bf16(tmem_base + O_COL, umma_desc_k_sw128(p2_addr) + 2 * kk,
+                      umma_desc_mn_sw128(v_addr + kk * 2048, 8192), idesc_o, true);
+        }
         umma_commit(&vempty[st]);
         umma_commit(pv_done);
       }
@@ -344,7 +361,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c0 = 0; c0 < PF_KEYS; c0 += 8) {
-        __nv_bfloat162 h[4];
+        __nv_bfloat162 h[4], h2[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           // (masked scores are -inf: exp2 gives zero)
@@ -352,10 +369,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           const float p1 = fast_exp2(fmaf(v[c0 + 2 * e + 1], p.scale_log2e, -mref));
           sum4[e] += p0 + p1;
           h[e] = __floats2bfloat162_rn(p0, p1);
+          if (SPLIT) {
+            const float2 back = __bfloat1622float2(h[e]);
+            h2[e] = __floats2bfloat162_rn(p0 - back.x, p1 - back.y);
+          }
         }
         const int ch = c0 >> 3;                                   // 8-key chunk index 0..7
         uint8_t* dst = p_s + r * 128 + ((ch ^ (r & 7)) << 4);
         *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(h);
+        if (SPLIT) *reinterpret_cast<uint4*>(dst + PBYTES) = *reinterpret_cast<uint4*>(h2);
       }
       l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       PF_CLK(5);
@@ -369,6 +391,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (ok) ok = mbar_wait(pv_done, (nblk - 1) & 1, abort_flag);
     if (ok) {
       tc_fence_after_sync();
+      if (p.sink) l += fast_exp2(fmaf(p.sink[head], 1.4426950408889634f, -((m == -INFINITY) ? 0.f : m)));
       const float inv = 1.0f / l;
       __nv_bfloat16* o = p.out + (size_t)(tok0 + r) * p.ldo + (size_t)head * HD;
 #pragma unroll
@@ -438,23 +461,24 @@ int make_map(CUtensorMap* m, const void* base, long long rows, int cols, long lo
   return r == CUDA_SUCCESS ? DLGO_OK : DLGO_ERR_DRIVER;
 }
 
-template <int HD>
+template <int HD, bool SPLIT = false>
 int launch_pf(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PfParams& p, int n_tiles,
               cudaStream_t stream) {
-  constexpr int SMEM = (HD / 64) * (16384 + 4 * 8192) + 16384 + 256;   // Q, 2 stages of K and of V, P, barriers
+  // Q, 2 stages of K and of V, P (two tiles when split), barriers
+  constexpr int SMEM = (HD / 64) * (16384 + 4 * 8192) + (SPLIT ? 2 : 1) * 16384 + 256;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          SMEM);
     if (e != cudaSuccess) return (int)e;
     // With heads of 64 three CTAs fit an SM (3 x 64 KB of shared memory, 3 x 128 columns of tensor
     // memory), with heads of 128 two: one's softmax runs beside the others' MMAs and maxima.  That
     // needs the largest carve-out.
-    cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout,
+    cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, SPLIT>, cudaFuncAttributePreferredSharedMemoryCarveout,
                          (int)cudaSharedmemCarveoutMaxShared);
     configured = true;
   }
-  launch_kernel(attention_prefill_tc_kernel<HD>, dim3(p.Hq, n_tiles), dim3(PF_THREADS), SMEM, stream, mq, mk, mv, p);
+  launch_kernel(attention_prefill_tc_kernel<HD, SPLIT>, dim3(p.Hq, n_tiles), dim3(PF_THREADS), SMEM, stream, mq, mk, mv, p);
   return launch_status();
 }
 
@@ -486,8 +510,41 @@ DLGO_EXPORT int dlgo_attention_prefill_tc(const void* q, int T, int ldq, const v
   p.tiles = tiles; p.seq_slot = seq_slot; p.token_pos = token_pos; p.page_table = page_table; p.max_pages = max_pages;
   p.out = (__nv_bfloat16*)out; p.ldo = ldo; p.Hq = Hq; p.Hkv = Hkv; p.window = window;
   p.scale_log2e = scale * 1.4426950408889634f;
+  p.sink = nullptr;
+  p.kv_rows = 0;
   if (hd == 64) return launch_pf<64>(mq, mk, mv, p, n_tiles, stream);
   return launch_pf<128>(mq, mk, mv, p, n_tiles, stream);
+}
+
+// The same attention over keys and values that were made for the step and lie as rows of tokens:
+// k, v [n_pages * 64, >= H * hd] bf16 with row stride ld_kv (head h at column h * hd; row page * 64 + key), every
+// query head with keys and values of its own; page_table [sequences, max_pages] maps a sequence's page index to a
+// page of these rows (-1: not there).  `sink` [H] fp32 or null.  `split` != 0: probabilities enter P V as two
+// bfloat16 terms (16 bits of mantissa).
+DLGO_EXPORT int dlgo_attention_prefill_tc_rows(const void* q, int T, int ldq, const void* k, const void* v, int n_pages,
+                                               int ld_kv, const int* page_table, int max_pages, const int* tiles,
+                                               int n_tiles, const int* seq_slot, const int* token_pos, void* out,
+                                               int ldo, int H, int hd, int window, float scale, const float* sink,
+                                               int split, cudaStream_t stream) {
+  if (T <= 0 || n_tiles <= 0) return DLGO_OK;
+  if (n_tiles > 65535 || n_pages <= 0) return DLGO_ERR_SIZE;
+  if (H <= 0 || !(hd == 64 || hd == 128) || H > 65535) return DLGO_ERR_SIZE;
+  if (ldo % 8 || ((uintptr_t)out & 15)) return DLGO_ERR_ALIGN;
+  CUtensorMap mq, mk, mv;
+  int st = make_map(&mq, q, T, H * hd, ldq, 128);
+  if (st != DLGO_OK) return st;
+  st = make_map(&mk, k, (long long)n_pages * 64, H * hd, ld_kv, 64);
+  if (st != DLGO_OK) return st;
+  st = make_map(&mv, v, (long long)n_pages * 64, H * hd, ld_kv, 64);
+  if (st != DLGO_OK) return st;
+  PfParams p;
+  p.tiles = tiles; p.seq_slot = seq_slot; p.token_pos = token_pos; p.page_table = page_table; p.max_pages = max_pages;
+  p.out = (__nv_bfloat16*)out; p.ldo = ldo; p.Hq = H; p.Hkv = H; p.window = window;
+  p.scale_log2e = scale * 1.4426950408889634f;
+  p.sink = sink;
+  p.kv_rows = 1;
+  if (hd == 64) return split ? launch_pf<64, true>(mq, mk, mv, p, n_tiles, stream) : launch_pf<64, false>(mq, mk, mv, p, n_tiles, stream);
+  return split ? launch_pf<128, true>(mq, mk, mv, p, n_tiles, stream) : launch_pf<128, false>(mq, mk, mv, p, n_tiles, stream);
 }
 
 DLGO_EXPORT int dlgo_attention_tc_error() {

@@ -324,6 +324,50 @@ def latent_attention(q: torch.Tensor, w_k: torch.Tensor, w_v: torch.Tensor, sink
     return out
 
 
+def latent_gather(pages: torch.Tensor, page_table: torch.Tensor, tmp_pages: torch.Tensor, n_tmp: int,
+                  seq_slot: torch.Tensor) -> torch.Tensor:
+    """Rows [n_tmp * page, rank] of the cached latents of the pages listed in ``tmp_pages`` [n_tmp, 3]
+    (sequence of the step, its page index, written rows); rows that are not written are zero."""
+    _need(pages, None, "pages")
+    for n, t in (("page_table", page_table), ("tmp_pages", tmp_pages), ("seq_slot", seq_slot)):
+        _need(t, torch.int32, n)
+    page_size, rank = pages.shape[-2], pages.shape[-1]
+    out = torch.empty((n_tmp * page_size, rank), dtype=pages.dtype, device=pages.device)
+    st = _lib("latent_attention").dlgo_latent_gather(_ptr(pages), _i(dtype_code(pages.dtype)), _ptr(page_table),
+                                                     _i(page_table.shape[1]), _i(page_size), _ptr(tmp_pages), _i(n_tmp),
+                                                     _ptr(seq_slot), _ptr(out), _i(rank), _stream())
+    _check(st, "latent_gather")
+    return out
+
+
+def attention_prefill_tc_rows(q: torch.Tensor, kv: torch.Tensor, k_col: int, v_col: int, n_pages: int,
+                              page_table: torch.Tensor, tiles: torch.Tensor, seq_rows: torch.Tensor,
+                              token_pos: torch.Tensor, num_heads: int, head_dim: int, scale: float, window: int = 0,
+                              sink: Optional[torch.Tensor] = None, split: bool = True) -> torch.Tensor:
+    """Prompt attention on the tensor cores over keys and values made for the step: ``kv`` [n_pages * 64, ld]
+    bf16 holds every head's keys from column ``k_col`` and values from ``v_col`` (head h at + h * head_dim),
+    row = page * 64 + key; ``page_table`` [sequences of the step, pages] maps a sequence's page index to a page
+    of these rows; ``seq_rows`` [sequences] names each sequence's row of that table.  ``sink`` [heads] joins the
+    denominator.  ``split``: probabilities enter P V as two bfloat16 terms.  Returns [T, heads * head_dim]."""
+    for n, t in (("q", q), ("kv", kv)):
+        if t.dtype != torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1:
+            raise KernelError(f"attention_prefill_tc_rows: {n} must be 2-D bfloat16 with unit inner stride")
+    for n, t in (("page_table", page_table), ("tiles", tiles), ("seq_rows", seq_rows), ("token_pos", token_pos)):
+        _need(t, torch.int32, n)
+    if sink is not None:
+        _need(sink, torch.float32, "sink")
+    T = q.shape[0]
+    out = torch.empty((T, num_heads * head_dim), dtype=torch.bfloat16, device=q.device)
+    es = kv.element_size()
+    st = _lib("attention_prefill_tc").dlgo_attention_prefill_tc_rows(
+        _ptr(q), _i(T), _i(q.stride(0)), _p(kv.data_ptr() + k_col * es), _p(kv.data_ptr() + v_col * es), _i(n_pages),
+        _i(kv.stride(0)), _ptr(page_table), _i(page_table.shape[1]), _ptr(tiles), _i(tiles.shape[0]), _ptr(seq_rows),
+        _ptr(token_pos), _ptr(out), _i(out.stride(0)), _i(num_heads), _i(head_dim), _i(window), _f(scale), _ptr(sink),
+        _i(1 if split else 0), _stream())
+    _check(st, "attention_prefill_tc_rows")
+    return out
+
+
 # ---------------------------------------------------------- lightning attention
 def lightning_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, tiles: torch.Tensor, n_seqs: int,
                    seq_slot: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, num_heads: int, qk_dim: int,
@@ -347,6 +391,40 @@ def lightning_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, tiles
                                                _ptr(out), _i(out.stride(0)), _i(num_heads), _i(qk_dim), _i(v_dim),
                                                _stream())
     _check(st, "lightning_scan")
+    return out
+
+
+def lightning_segments_takes(qk_dim: int) -> bool:
+    """Whether the segment kernels (the state's columns in registers, segments side by side) take this qk size."""
+    return qk_dim in (32, 64, 128)
+
+
+def lightning_segments(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, tiles: torch.Tensor, n_tiles: int,
+                       direct: bool, seq_slot: torch.Tensor, decay: torch.Tensor, state: torch.Tensor,
+                       scratch: Optional[torch.Tensor], num_heads: int, qk_dim: int, v_dim: int) -> torch.Tensor:
+    """:func:`lightning_scan` with every sequence's tokens cut into consecutive segments (``tiles`` [n_tiles, 3],
+    a sequence's segments in token order) that run side by side: each first computes its own end state from
+    zero, then starts from the decayed sum of what lies before it.  ``direct``: one segment per sequence (no
+    first pass); else ``scratch`` holds 2 * n_tiles * H * qk_dim * v_dim floats."""
+    if proj.dtype != torch.float32 or proj.dim() != 2 or proj.stride(1) != 1:
+        raise KernelError("lightning_segments: proj must be 2-D float32 with unit inner stride")
+    _need(tiles, torch.int32, "tiles")
+    _need(seq_slot, torch.int32, "seq_slot")
+    _need(decay, torch.float32, "decay")
+    _need(state, torch.float32, "state")
+    if tuple(state.shape[1:]) != (num_heads, qk_dim, v_dim) or decay.numel() != num_heads:
+        raise KernelError("lightning_segments: state must be [slots, heads, qk_dim, v_dim] and decay [heads]")
+    if not direct:
+        need = 2 * n_tiles * num_heads * qk_dim * v_dim
+        if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
+            raise KernelError(f"lightning_segments: {n_tiles} segments need {need} floats of scratch")
+    T = proj.shape[0]
+    out = torch.empty((T, num_heads * v_dim), dtype=torch.float32, device=proj.device)
+    st = _lib("lightning").dlgo_lightning_segments(
+        _ptr(proj), _i(proj.stride(0)), _i(q_off), _i(k_off), _i(v_off), _ptr(tiles), _i(n_tiles),
+        _i(1 if direct else 0), _ptr(seq_slot), _ptr(decay), _ptr(state), _ptr(scratch), _ptr(out), _i(out.stride(0)),
+        _i(num_heads), _i(qk_dim), _i(v_dim), _stream())
+    _check(st, "lightning_segments", 1 if direct else 2)
     return out
 
 

@@ -52,6 +52,24 @@ __global__ void latent_norm_append_kernel(const float* __restrict__ proj, int ld
   for (int i = threadIdx.x; i < n; i += blockDim.x) dst[i] = from_float<T>(x[i] * sc * w[i]);
 }
 
+// Latents of the pages a prompt step attends, gathered into rows [n_tmp * page_size, rank] (row = temporary page
+// * page_size + place in the page) for the contraction that makes the step's keys and values.  `tmp_pages`
+// [n_tmp, 3]: (sequence of the step, its page index, rows of the page that are written); other rows are zero.
+template <typename T>
+__global__ void latent_gather_kernel(const T* __restrict__ pages, const int* __restrict__ page_table, int max_pages,
+                                     int page_size, const int* __restrict__ tmp_pages,
+                                     const int* __restrict__ seq_slot, T* __restrict__ out, int rank) {
+  pdl_launch_dependents();
+  const int tp = blockIdx.x;
+  const int seq = tmp_pages[tp * 3], lp = tmp_pages[tp * 3 + 1], valid = tmp_pages[tp * 3 + 2];
+  const int page = page_table[(size_t)seq_slot[seq] * max_pages + lp];
+  pdl_wait();
+  const T* src = pages + (size_t)(page < 0 ? 0 : page) * page_size * rank;
+  T* dst = out + (size_t)tp * page_size * rank;
+  const int n_valid = page < 0 ? 0 : valid * rank;
+  for (int i = threadIdx.x; i < page_size * rank; i += blockDim.x) dst[i] = i < n_valid ? src[i] : from_float<T>(0.f);
+}
+
 __device__ __forceinline__ float2 load_pair(const float* p) { return *reinterpret_cast<const float2*>(p); }
 __device__ __forceinline__ float2 load_pair(const __nv_bfloat16* p) {
   return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
@@ -203,6 +221,22 @@ DLGO_EXPORT int dlgo_latent_norm_append(const float* proj, int ld, int T_tokens,
     launch_kernel(latent_norm_append_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, proj, ld, kv_off, kv_rank,
                   w_kv, q_off, q_rank, w_q, (__nv_bfloat16*)cq, eps, token_pos, token_seq, seq_slot, page_table,
                   max_pages, (__nv_bfloat16*)pages, page_size, write_cache);
+  else
+    return DLGO_ERR_DTYPE;
+  return launch_status();
+}
+
+DLGO_EXPORT int dlgo_latent_gather(const void* pages, int dtype, const int* page_table, int max_pages, int page_size,
+                                   const int* tmp_pages, int n_tmp, const int* seq_slot, void* out, int rank,
+                                   cudaStream_t stream) {
+  if (n_tmp <= 0) return DLGO_OK;
+  if (rank <= 0 || page_size <= 0) return DLGO_ERR_SIZE;
+  if (dtype == DLGO_F32)
+    launch_kernel(latent_gather_kernel<float>, dim3(n_tmp), dim3(256), 0, stream, (const float*)pages, page_table,
+                  max_pages, page_size, tmp_pages, seq_slot, (float*)out, rank);
+  else if (dtype == DLGO_BF16)
+    launch_kernel(latent_gather_kernel<__nv_bfloat16>, dim3(n_tmp), dim3(256), 0, stream, (const __nv_bfloat16*)pages,
+                  page_table, max_pages, page_size, tmp_pages, seq_slot, (__nv_bfloat16*)out, rank);
   else
     return DLGO_ERR_DTYPE;
   return launch_status();

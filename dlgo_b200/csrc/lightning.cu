@@ -62,9 +62,167 @@ __global__ void lightning_scan_kernel(const float* __restrict__ proj, int ld, in
   for (int i = threadIdx.x; i < dk * dv; i += blockDim.x) st[i] = S[i];
 }
 
+// Common qk sizes: a thread keeps its column of the state in registers, and a sequence's tokens of one step
+// are cut into segments that run side by side.
+//   pass 1 (LOCAL): every segment runs from a zero state and leaves its end state L_i; a sequence's first
+//                   segment also copies the sequence's stored state S_in aside
+//   pass 2:         segment i starts from  lambda^(n_0 + .. + n_(i-1)) S_in + sum_(j<i) lambda^(n_(j+1) + .. + n_(i-1)) L_j,
+//                   walks its tokens and writes their outputs; the last segment stores the sequence's new state
+// With DIRECT (one segment per sequence: decoding, short prompts) pass 2 runs alone and starts from S_in.
+template <int DK, bool LOCAL, bool DIRECT>
+__global__ void __launch_bounds__(128)
+lightning_segments_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off,
+                          const int* __restrict__ tiles, int n_tiles, const int* __restrict__ seq_slot,
+                          const float* __restrict__ decay, float* __restrict__ state, float* __restrict__ local,
+                          float* __restrict__ start_copy, float* __restrict__ out, int ldo, int H, int dv) {
+  pdl_launch_dependents();
+  __shared__ __align__(16) float qk[2][2 * DK];
+  const int tile = blockIdx.x, h = blockIdx.y;
+  const int e = blockIdx.z * blockDim.x + threadIdx.x;          // this thread's column of the state
+  const bool live = e < dv;
+  const int seq = tiles[tile * 3 + 0], first = tiles[tile * 3 + 1], count = tiles[tile * 3 + 2];
+  const int slot = seq_slot[seq];
+  const float lam = decay[h];
+  int t0 = tile;                                                 // the sequence's first segment
+  while (t0 > 0 && tiles[(t0 - 1) * 3] == seq) --t0;
+  const bool last = tile + 1 == n_tiles || tiles[(tile + 1) * 3] != seq;
+  float* st = state + ((size_t)slot * H + h) * DK * dv;
+  const size_t seg_elems = (size_t)H * DK * dv;
+  pdl_wait();
+  float S[DK];
+  if (LOCAL) {
+#pragma unroll
+    for (int i = 0; i < DK; ++i) S[i] = 0.f;
+    if (tile == t0 && live)
+      for (int i = 0; i < DK; ++i) start_copy[(size_t)tile * seg_elems + ((size_t)h * DK + i) * dv + e] = st[(size_t)i * dv + e];
+  } else if (DIRECT) {
+#pragma unroll
+    for (int i = 0; i < DK; ++i) S[i] = live ? st[(size_t)i * dv + e] : 0.f;
+  } else {
+    int before = 0;                                              // tokens of this step ahead of the segment
+    for (int j = t0; j < tile; ++j) before += tiles[j * 3 + 2];
+    const float f0 = powf(lam, (float)before);
+#pragma unroll
+    for (int i = 0; i < DK; ++i)
+      S[i] = live ? f0 * start_copy[(size_t)t0 * seg_elems + ((size_t)h * DK + i) * dv + e] : 0.f;
+    int after = before;
+    for (int j = t0; j < tile; ++j) {
+      after -= tiles[j * 3 + 2];                                 // tokens between segment j's end and this one's start
+      const float f = powf(lam, (float)after);
+      const float* L = local + (size_t)j * seg_elems + (size_t)h * DK * dv;
+      if (live) {
+#pragma unroll
+        for (int i = 0; i < DK; ++i) S[i] = fmaf(f, L[(size_t)i * dv + e], S[i]);
+      }
+    }
+  }
+  // q and k of a token: 2 DK numbers, fetched by the block's threads into registers one token ahead and put
+  // into shared memory (through silu) behind the current token's products
+  constexpr int PER_T = (2 * DK + 127) / 128;                    // (blocks have 128 threads)
+  float raw[PER_T];
+  auto fetch = [&](int tok) {
+    const float* row = proj + (size_t)tok * ld;
+#pragma unroll
+    for (int j = 0; j < PER_T; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      raw[j] = i < 2 * DK ? row[i < DK ? q_off + h * DK + i : k_off + h * DK + (i - DK)] : 0.f;
+    }
+  };
+  auto put = [&](float* buf) {
+#pragma unroll
+    for (int j = 0; j < PER_T; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      if (i < 2 * DK) buf[i] = silu_f(raw[j]);
+    }
+  };
+  fetch(first);
+  put(qk[0]);
+  const float* vcol = proj + v_off + h * dv + (live ? e : 0);
+  float v_raw = vcol[(size_t)first * ld];
+  __syncthreads();
+  for (int n = 0; n < count; ++n) {
+    const float* cur = qk[n & 1];
+    const float v = live ? silu_f(v_raw) : 0.f;
+    const bool more = n + 1 < count;
+    if (more) {
+      v_raw = vcol[(size_t)(first + n + 1) * ld];
+      fetch(first + n + 1);
+    }
+    float o = 0.f;
+#pragma unroll
+    for (int i = 0; i < DK; i += 4) {
+      const float4 k4 = *reinterpret_cast<const float4*>(cur + DK + i);
+      S[i] = fmaf(lam, S[i], k4.x * v);
+      S[i + 1] = fmaf(lam, S[i + 1], k4.y * v);
+      S[i + 2] = fmaf(lam, S[i + 2], k4.z * v);
+      S[i + 3] = fmaf(lam, S[i + 3], k4.w * v);
+      if (!LOCAL) {
+        const float4 q4 = *reinterpret_cast<const float4*>(cur + i);
+        o = fmaf(S[i], q4.x, o);
+        o = fmaf(S[i + 1], q4.y, o);
+        o = fmaf(S[i + 2], q4.z, o);
+        o = fmaf(S[i + 3], q4.w, o);
+      }
+    }
+    if (more) put(qk[(n + 1) & 1]);
+    if (!LOCAL && live) out[(size_t)(first + n) * ldo + h * dv + e] = o;
+    __syncthreads();
+  }
+  if (!live) return;
+  if (LOCAL) {
+    float* L = local + (size_t)tile * seg_elems + (size_t)h * DK * dv;
+#pragma unroll
+    for (int i = 0; i < DK; ++i) L[(size_t)i * dv + e] = S[i];
+  } else if (last) {
+#pragma unroll
+    for (int i = 0; i < DK; ++i) st[(size_t)i * dv + e] = S[i];
+  }
+}
+
+template <int DK>
+static int launch_segments(const float* proj, int ld, int q_off, int k_off, int v_off, const int* tiles, int n_tiles,
+                           int direct, const int* seq_slot, const float* decay, float* state, float* scratch,
+                           float* out, int ldo, int H, int dv, cudaStream_t stream) {
+  const dim3 grid(n_tiles, H, (dv + 127) / 128), block(128);
+  float* local = scratch;
+  float* start_copy = scratch ? scratch + (size_t)n_tiles * H * DK * dv : nullptr;
+  if (direct) {
+    launch_kernel(lightning_segments_kernel<DK, false, true>, grid, block, 0, stream, proj, ld, q_off, k_off, v_off,
+                  tiles, n_tiles, seq_slot, decay, state, local, start_copy, out, ldo, H, dv);
+    return launch_status();
+  }
+  if (!scratch) return DLGO_ERR_SIZE;
+  launch_kernel(lightning_segments_kernel<DK, true, false>, grid, block, 0, stream, proj, ld, q_off, k_off, v_off, tiles,
+                n_tiles, seq_slot, decay, state, local, start_copy, out, ldo, H, dv);
+  int st = launch_status();
+  if (st != DLGO_OK) return st;
+  launch_kernel(lightning_segments_kernel<DK, false, false>, grid, block, 0, stream, proj, ld, q_off, k_off, v_off, tiles,
+                n_tiles, seq_slot, decay, state, local, start_copy, out, ldo, H, dv);
+  return launch_status();
+}
+
 }  // namespace dlgo
 
 using namespace dlgo;
+
+// 1 if the segment kernels take this qk size (the state's column in registers)
+DLGO_EXPORT int dlgo_lightning_segments_takes(int dk) { return dk == 32 || dk == 64 || dk == 128; }
+
+// As dlgo_lightning_scan, with `tiles` [n_tiles, 3] cutting every sequence's tokens into consecutive segments
+// (a sequence's segments side by side in the table, in token order).  `direct`: every sequence has exactly one
+// segment.  Otherwise `scratch` holds 2 * n_tiles * H * dk * dv floats.
+DLGO_EXPORT int dlgo_lightning_segments(const float* proj, int ld, int q_off, int k_off, int v_off, const int* tiles,
+                                        int n_tiles, int direct, const int* seq_slot, const float* decay,
+                                        float* state, float* scratch, float* out, int ldo, int H, int dk, int dv,
+                                        cudaStream_t stream) {
+  if (n_tiles <= 0) return DLGO_OK;
+  if (H <= 0 || dv <= 0 || n_tiles > 65535 * 32) return DLGO_ERR_SIZE;
+#define SEG_ARGS proj, ld, q_off, k_off, v_off, tiles, n_tiles, direct, seq_slot, decay, state, scratch, out, ldo, H, dv, stream
+  if (dk == 32) return launch_segments<32>(SEG_ARGS);
+  if (dk == 64) return launch_segments<64>(SEG_ARGS);
+  if (dk == 128) return launch_segments<128>(SEG_ARGS);
+  return DLGO_ERR_SIZE;
+}
 
 // proj [T, ld] fp32; tiles [n_seqs, 3] (sequence, first packed token, count): one row per sequence of the step;
 // state [slots, H, dk, dv] fp32; out [T, ldo] fp32 (heads side by side, dv each)

@@ -110,8 +110,18 @@ class DecodeGraph:
         if saved is not None:
             eng.cache.state.restore(slots, saved)
         before = kernels.LAUNCHES
-        with torch.cuda.graph(self.graph, pool=eng.graph_pool()):
-            self.logits = eng.model.forward(self.ctx, eng.cache, self.want_rows)
+        # An engine that is no longer used may be collected at any allocation; destroying ITS captured graphs
+        # while this capture is open would invalidate it.  Collect now, and not again until the capture ends.
+        import gc
+        gc.collect()
+        was_on = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self.graph, pool=eng.graph_pool()):
+                self.logits = eng.model.forward(self.ctx, eng.cache, self.want_rows)
+        finally:
+            if was_on:
+                gc.enable()
         self.kernels_per_replay = kernels.LAUNCHES - before
         self._exec = self.graph.raw_cuda_graph_exec()
 

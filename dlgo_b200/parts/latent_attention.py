@@ -16,6 +16,7 @@ norms are taken in fp32; scores, softmax and the weighted sum are fp32 in every 
 """
 from __future__ import annotations
 
+import os
 from typing import Any, Callable, Dict, Mapping, Optional
 
 import torch
@@ -28,6 +29,10 @@ from .registry import MIXERS
 _NAMES = {"q": "q_proj.weight", "q_down": "q_a_proj.weight", "q_norm": "q_a_norm.weight", "q_up": "q_b_proj.weight",
           "kv_down": "kv_a_proj.weight", "kv_norm": "kv_a_norm.weight", "k_up": "k_b_proj.weight",
           "v_up": "v_b_proj.weight", "sink": "sinks", "out": "o_proj.weight"}
+
+
+# prompt steps of at least this many tokens make the step's keys and values and run on the tensor cores
+PROMPT_TC_MIN_TOKENS = int(os.environ.get("DLGO_LATENT_TC_MIN_TOKENS", 64))
 
 
 class LatentAttention(Mixer):
@@ -92,8 +97,11 @@ class LatentAttention(Mixer):
         if self.q_rank is not None:
             self.q_norm = get(n["q_norm"]).to(torch.float32).contiguous()
             self.w_q_up = Linear(get(n["q_up"]), runtime)
-        self.w_k_up = runtime.compute_copy(get(n["k_up"])).contiguous()
-        self.w_v_up = runtime.compute_copy(get(n["v_up"])).contiguous()
+        # one matrix [Wk; Wv]: the per-token kernel reads its halves, a prompt step multiplies by all of it
+        self.w_kv_up = Linear(torch.cat([runtime.compute_copy(get(n["k_up"])), runtime.compute_copy(get(n["v_up"]))],
+                                        dim=0), runtime)
+        self.w_k_up = self.w_kv_up.weight[:self.n_heads * self.qk_dim]
+        self.w_v_up = self.w_kv_up.weight[self.n_heads * self.qk_dim:]
         if self.has_sink:
             self.sink = get(n["sink"]).to(torch.float32).contiguous()
         self.wo = Linear(get(n["out"]), runtime)
@@ -107,10 +115,54 @@ class LatentAttention(Mixer):
                                   ctx.token_pos, ctx.token_seq, ctx.seq_slot, cache.page_table, cache.keys,
                                   cache.writes)
         q = self.w_q_up(cq, STORE) if self.q_rank is not None else proj[:, :n_q]
+        if self.prompt_on_tensor_cores(ctx, cache):
+            out = self._prompt_tc(q, ctx, cache)
+            self.wo(out, ADD_F32, residual)
+            return
         out = K.latent_attention(q, self.w_k_up, self.w_v_up, self.sink, cache.keys, cache.page_table, ctx.seq_slot,
                                  ctx.token_seq, ctx.token_pos, self.n_heads, self.qk_dim, self.v_dim, self.scale,
                                  self.window or 0)
         self.wo(out, ADD_F32, residual)
+
+
+    # ------------------------------------------------------- prompts on the tensor cores
+    def prompt_on_tensor_cores(self, ctx: Any, cache: Any) -> bool:
+        """A prompt step in bfloat16 of enough tokens, heads of 64 or 128 with equal key and value sizes."""
+        return (not ctx.decode and ctx.n_tokens >= PROMPT_TC_MIN_TOKENS and cache.keys.dtype == torch.bfloat16 and
+                self.qk_dim == self.v_dim and
+                K.attention_prefill_tc_takes(torch.bfloat16, self.qk_dim, cache.page_size))
+
+    def _prompt_tc(self, q: torch.Tensor, ctx: Any, cache: Any) -> torch.Tensor:
+        """Keys and values of every position the step's tokens see, made from the cached latents by one
+        contraction with [Wk; Wv], then the tensor-core prompt attention over those rows (scores fp32 in tensor
+        memory, softmax fp32, probabilities as two bfloat16 terms)."""
+        ps = cache.page_size
+        pages, table_rows = [], []
+        for i, (start, n) in enumerate(zip(ctx.seq_start_host, ctx.seq_ntok_host)):
+            first = (max(0, start - self.window + 1) if self.window else 0) // ps
+            last = (start + n - 1) // ps
+            row = [-1] * (last + 1)
+            for lp in range(first, last + 1):
+                row[lp] = len(pages)
+                pages.append((i, lp, min(ps, start + n - lp * ps)))
+            table_rows.append(row)
+        width = max(len(r) for r in table_rows)
+        meta = torch.tensor([v for p in pages for v in p] + [v for r in table_rows for v in r + [-1] * (width - len(r))],
+                            dtype=torch.int32).to(q.device, non_blocking=True)
+        n_tmp = len(pages)
+        tmp_pages = meta[:3 * n_tmp].view(n_tmp, 3)
+        tmp_table = meta[3 * n_tmp:].view(len(table_rows), width)
+        seq_rows = ctx._scratch.get("seq_rows")             # sequence i of the step reads row i of the table
+        if seq_rows is None or seq_rows.numel() < ctx.n_seqs:
+            seq_rows = ctx._scratch["seq_rows"] = torch.arange(max(ctx.n_seqs, 64), dtype=torch.int32, device=q.device)
+        latents = K.latent_gather(cache.keys, cache.page_table, tmp_pages, n_tmp, ctx.seq_slot)
+        kv = self.w_kv_up(latents, STORE)                      # [pages * 64, H * (qk_dim + v_dim)]
+        if q.dtype != torch.bfloat16:
+            q = K.bias_act(q, None, K.ACT_NONE, torch.bfloat16)
+        tiles, _, _ = ctx.tiles(K.PREFILL_TC_TILE, heaviest_first=True)
+        return K.attention_prefill_tc_rows(q, kv, 0, self.n_heads * self.qk_dim, n_tmp, tmp_table, tiles, seq_rows,
+                                           ctx.token_pos, self.n_heads, self.qk_dim, self.scale, self.window or 0,
+                                           self.sink)
 
 
 MIXERS.register("latent_attention", LatentAttention)

@@ -23,6 +23,7 @@ from .registry import MIXERS
 _NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "gate": "g_proj.weight",
           "out": "o_proj.weight", "norm": "norm.weight"}
 _WHOLE_SEQUENCE = 1 << 30      # a "tile" as long as any sequence's tokens of one step
+SEGMENT = 128                  # tokens of a segment where a prompt's segments run side by side
 
 
 class LightningAttention(Mixer):
@@ -67,8 +68,16 @@ class LightningAttention(Mixer):
             raise RuntimeError("lightning attention needs its state")
         H, dk, dv = self.n_heads, self.qk_dim, self.v_dim
         proj = self.w_in(x, STORE_F32)                      # [T, 2 H dk + 2 H dv] fp32
-        tiles, n_seqs, _ = ctx.tiles(1 if ctx.decode else _WHOLE_SEQUENCE)
-        o = K.lightning_scan(proj, 0, H * dk, 2 * H * dk, tiles, n_seqs, ctx.seq_slot, self.decay, state, H, dk, dv)
+        if K.lightning_segments_takes(dk):
+            # the state's columns in registers; a prompt's segments side by side
+            tiles, n_tiles, _ = ctx.tiles(1 if ctx.decode else SEGMENT)
+            direct = ctx.decode or n_tiles == ctx.n_seqs
+            scratch = None if direct else ctx.scratch("lightning_segments", 2 * n_tiles * H * dk * dv)
+            o = K.lightning_segments(proj, 0, H * dk, 2 * H * dk, tiles, n_tiles, direct, ctx.seq_slot, self.decay,
+                                     state, scratch, H, dk, dv)
+        else:
+            tiles, n_seqs, _ = ctx.tiles(1 if ctx.decode else _WHOLE_SEQUENCE)
+            o = K.lightning_scan(proj, 0, H * dk, 2 * H * dk, tiles, n_seqs, ctx.seq_slot, self.decay, state, H, dk, dv)
         a = K.gated_rmsnorm(o, proj[:, 2 * H * dk + H * dv:], self.norm, self.eps, self.wo.weight.dtype)
         self.wo(a, ADD_F32, residual)
 

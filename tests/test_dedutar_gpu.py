@@ -225,6 +225,67 @@ def test_window_edge(window, dtype):
         assert float(row_error(refs[window - 1][-1:], refs[window][-1:])) > 0.2     # the edge shows in the oracle
 
 
+@pytest.mark.parametrize("dim", [64, 128])
+@pytest.mark.parametrize("kind, window", [("latent_attention_2", None), ("latent_attention", 100),
+                                          ("latent_attention", 64), ("latent_attention", 1000)])
+def test_latent_prompts_on_the_tensor_cores(kind, window, dim):
+    """bfloat16 prompt steps with heads of 64 and 128 make the step's keys and values and run on the tensor
+    cores: whole prompts, portions that read back what earlier portions cached (also behind a window whose pages
+    were given back), unequal batches, a sink, and one far key that carries the answer."""
+    from dlgo_b200.csrc import kernels as K
+    dtype = "bfloat16"
+    m = {"heads": 3, "dim": dim, "vdim": dim, "kv_rank": 96, "scale": dim ** -0.5}
+    if kind == "latent_attention":
+        m.update(q_rank=48, mask={"size": window})
+    cfg = one_layer({"type": kind, "mixer": m}, streams=2, width=64)
+    w = make_weights(cfg, 9, sharpen=16.0)
+    b, a, f = standing_out(cfg, w)
+    n = 330
+    tokens = random_tokens(n, cfg["vocab"], 4)
+    ref = plain_of(cfg, w, tokens)
+    eng = engine_of(cfg, w, dtype)
+    K.profile_start()
+    got = run_whole(eng, tokens)
+    names = {k for k, _, _ in K.profile_stop()}
+    assert "attention_prefill_tc_rows" in names and "latent_attention" not in names
+    assert_rows(got, ref, dtype, "whole prompt")
+    for cuts in ([130, 200], [64, 64, 202], [100, 70, 96, 64], [329, 1]):
+        s = eng.take_slot()
+        out, at = [], 0
+        for c in cuts:
+            out.append(eng.step([s], [tokens[at:at + c]], [list(range(c))]).clone())
+            at += c
+        eng.free_slot(s)
+        assert_rows(torch.cat(out), ref, dtype, f"portions {cuts}")
+    # unequal prompts in one step
+    lens = [70, 330, 129, 64]
+    slots = [eng.take_slot() for _ in lens]
+    out = eng.step(slots, [tokens[:k] for k in lens], [list(range(k)) for k in lens])
+    off = 0
+    for k in lens:
+        assert_rows(out[off:off + k], ref[:k], dtype, f"a prompt of {k} in a batch")
+        off += k
+    for s in slots:
+        eng.free_slot(s)
+    # the key that carries the answer: far back, at a page's border, just inside and just outside the window
+    places = [0, 63, 64, 191] if window is None else [n - window, n - window + 1]
+    for place in places:
+        if place < 0:
+            continue
+        seq = [f] * n + [b]
+        seq[place] = a
+        r2 = plain_of(cfg, w, seq)
+        s = eng.take_slot()
+        got = eng.step([s], [seq], [[n - 1, n]])
+        eng.free_slot(s)
+        assert_rows(got, r2[n - 1:], dtype, f"key at {place}")
+    if window is not None and window < n:
+        inside, outside = [f] * n + [b], [f] * n + [b]
+        inside[n - window + 1] = a
+        outside[n - window] = a
+        assert float(row_error(plain_of(cfg, w, inside)[-1:], plain_of(cfg, w, outside)[-1:])) > 0.2
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_sink_counts_once_and_unscaled(dtype):
     layer = {"type": "latent_attention_2", "mixer": {"heads": 4, "dim": 8, "vdim": 8, "kv_rank": 16, "scale": 0.5}}
@@ -246,15 +307,18 @@ def test_sink_counts_once_and_unscaled(dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("decay", [[1.0, 0.0, 0.5], [0.999, 0.9, 0.99]])
-def test_lightning_state_is_carried(decay, dtype):
-    layer = {"type": "lightning", "mixer": {"heads": 3, "dim": 16, "vdim": 24, "decay": decay}}
+@pytest.mark.parametrize("dim, vdim", [(16, 24), (32, 40), (64, 160), (128, 16)])
+def test_lightning_state_is_carried(dim, vdim, decay, dtype):
+    """qk sizes of both kernels (the state in shared memory; in registers with a prompt cut into segments that
+    run side by side), value sizes below, at and above a block's columns."""
+    layer = {"type": "lightning", "mixer": {"heads": 3, "dim": dim, "vdim": vdim, "decay": decay}}
     cfg = one_layer(layer, streams=2)
     w = make_weights(cfg, 8)
-    tokens = random_tokens(150, cfg["vocab"], 2)
+    tokens = random_tokens(300, cfg["vocab"], 2)
     ref = plain_of(cfg, w, tokens)
     eng = engine_of(cfg, w, dtype)
     assert_rows(run_whole(eng, tokens), ref, dtype, "whole")
-    for cuts in ([1, 1, 2, 3, 60, 64, 19], [149, 1], [2] * 75, [64, 64, 22]):
+    for cuts in ([1, 1, 2, 3, 60, 64, 169], [299, 1], [2] * 150, [129, 128, 43], [10, 290]):
         s = eng.take_slot()
         got, at = [], 0
         for c in cuts:
