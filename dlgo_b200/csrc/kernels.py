@@ -324,6 +324,46 @@ def latent_attention(q: torch.Tensor, w_k: torch.Tensor, w_v: torch.Tensor, sink
     return out
 
 
+def latent_attention_few_takes(dtype: torch.dtype, rank: int) -> bool:
+    """Whether the three-launch kernels take this rank (a latent row is read 16 bytes at a time)."""
+    v = 4 if dtype == torch.float32 else 8
+    return rank % v == 0 and rank <= 256 * v
+
+
+def latent_attention_few(q: torch.Tensor, w_k: torch.Tensor, w_v: torch.Tensor, sink: Optional[torch.Tensor],
+                         pages: torch.Tensor, page_table: torch.Tensor, seq_slot: torch.Tensor,
+                         token_seq: torch.Tensor, token_pos: torch.Tensor, num_heads: int, qk_dim: int, v_dim: int,
+                         scale: float, window: int, n_slices: int, q_lat: torch.Tensor,
+                         parts: torch.Tensor) -> torch.Tensor:
+    """:func:`latent_attention` for steps of few tokens, as three launches that each fill the GPU: the queries
+    into latent space (``q_lat`` [T, H, rank] fp32 scratch), the softmax over every token's visible latents cut
+    into ``n_slices`` slices (``parts`` [T, H, n_slices, rank + 2] fp32 scratch), and the slices' meeting, the
+    sink and the way out through Wv."""
+    _need(pages, None, "pages")
+    _need(w_k, pages.dtype, "w_k")
+    _need(w_v, pages.dtype, "w_v")
+    if q.dtype not in (torch.float32, pages.dtype) or q.dim() != 2 or q.stride(1) != 1:
+        raise KernelError("latent_attention_few: q must be 2-D, float32 or the cache's type, with unit inner stride")
+    if sink is not None:
+        _need(sink, torch.float32, "sink")
+    for n, t in (("page_table", page_table), ("seq_slot", seq_slot), ("token_seq", token_seq), ("token_pos", token_pos)):
+        _need(t, torch.int32, n)
+    T, rank = q.shape[0], pages.shape[-1]
+    if tuple(w_k.shape) != (num_heads * qk_dim, rank) or tuple(w_v.shape) != (num_heads * v_dim, rank):
+        raise KernelError("latent_attention_few: the up-projections do not fit heads, sizes and rank")
+    if q_lat.dtype != torch.float32 or q_lat.numel() < T * num_heads * rank or parts.dtype != torch.float32 or \
+            parts.numel() < T * num_heads * n_slices * (rank + 2):
+        raise KernelError("latent_attention_few: scratch too small")
+    out = torch.empty((T, num_heads * v_dim), dtype=pages.dtype, device=q.device)
+    st = _lib("latent_attention").dlgo_latent_attention_few(
+        _ptr(q), _i(1 if q.dtype == torch.float32 else 0), _i(q.stride(0)), _ptr(w_k), _ptr(w_v), _ptr(sink),
+        _ptr(pages), _i(dtype_code(pages.dtype)), _ptr(page_table), _i(page_table.shape[1]), _i(pages.shape[-2]),
+        _ptr(seq_slot), _ptr(token_seq), _ptr(token_pos), _ptr(out), _i(out.stride(0)), _i(T), _i(num_heads),
+        _i(qk_dim), _i(v_dim), _i(rank), _f(scale), _i(window), _i(n_slices), _ptr(q_lat), _ptr(parts), _stream())
+    _check(st, "latent_attention_few", 3)
+    return out
+
+
 def latent_gather(pages: torch.Tensor, page_table: torch.Tensor, tmp_pages: torch.Tensor, n_tmp: int,
                   seq_slot: torch.Tensor) -> torch.Tensor:
     """Rows [n_tmp * page, rank] of the cached latents of the pages listed in ``tmp_pages`` [n_tmp, 3]

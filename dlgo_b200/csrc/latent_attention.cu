@@ -55,6 +55,8 @@ __global__ void latent_norm_append_kernel(const float* __restrict__ proj, int ld
 // Latents of the pages a prompt step attends, gathered into rows [n_tmp * page_size, rank] (row = temporary page
 // * page_size + place in the page) for the contraction that makes the step's keys and values.  `tmp_pages`
 // [n_tmp, 3]: (sequence of the step, its page index, rows of the page that are written); other rows are zero.
+constexpr int GATHER_PARTS = 8;     // blocks that share a page
+
 template <typename T>
 __global__ void latent_gather_kernel(const T* __restrict__ pages, const int* __restrict__ page_table, int max_pages,
                                      int page_size, const int* __restrict__ tmp_pages,
@@ -66,8 +68,18 @@ __global__ void latent_gather_kernel(const T* __restrict__ pages, const int* __r
   pdl_wait();
   const T* src = pages + (size_t)(page < 0 ? 0 : page) * page_size * rank;
   T* dst = out + (size_t)tp * page_size * rank;
-  const int n_valid = page < 0 ? 0 : valid * rank;
-  for (int i = threadIdx.x; i < page_size * rank; i += blockDim.x) dst[i] = i < n_valid ? src[i] : from_float<T>(0.f);
+  const int total = page_size * rank, n_valid = page < 0 ? 0 : valid * rank;
+  const int per = (total + GATHER_PARTS - 1) / GATHER_PARTS;
+  const int lo = blockIdx.y * per, hi = min(total, lo + per);
+  constexpr int V = 16 / (int)sizeof(T);                         // elements of a 16-byte piece
+  if ((rank % V) == 0 && (per % V) == 0 && ((uintptr_t)pages & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+    // written rows end at a multiple of `rank`, so a 16-byte piece is wholly written or wholly not
+    for (int i = lo + threadIdx.x * V; i < hi; i += blockDim.x * V)
+      *reinterpret_cast<uint4*>(dst + i) = i < n_valid ? __ldg(reinterpret_cast<const uint4*>(src + i))
+                                                        : make_uint4(0u, 0u, 0u, 0u);
+    return;
+  }
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) dst[i] = i < n_valid ? src[i] : from_float<T>(0.f);
 }
 
 __device__ __forceinline__ float2 load_pair(const float* p) { return *reinterpret_cast<const float2*>(p); }
@@ -184,6 +196,295 @@ latent_attention_kernel(const void* __restrict__ q, int q_is_f32, int ldq, const
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Few tokens (decoding): three launches, each with enough blocks for the whole GPU.
+//   absorb   q~[t, h, :] = (Wk_h)^T q[t, h, :]: a block per (head, 32 latent columns), its warps sharing the rows, reads its part of Wk
+//            once for all tokens of the step
+//   partial  a block per (token, head, slice of the visible keys): online softmax over the latents in fp32;
+//            keys go round the block's warps, four in flight per warp.  Leaves (max, sum, weighted latent)
+//   out      a block per (head, 8 value columns): the slices of a token meet in slice order, the sink joins the
+//            denominator, and the weighted latent goes through its rows of Wv_h
+constexpr int AB_TOKENS = 8;    // tokens whose sums a thread of `absorb` keeps at a time
+
+constexpr int AB_COLS = 32;     // latent columns of a block (a lane each); its four warps share the rows of Wk_h
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+latent_absorb_kernel(const void* __restrict__ q, int q_is_f32, int ldq, const T* __restrict__ w_k,
+                     float* __restrict__ q_lat, int n_tokens, int H, int dk, int rank) {
+  pdl_launch_dependents();
+  extern __shared__ float s_q[];                                // [AB_TOKENS][dk], then [4][AB_TOKENS][AB_COLS]
+  float* s_part = s_q + AB_TOKENS * dk;
+  const int h = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int r = blockIdx.y * AB_COLS + lane;
+  const int t0 = blockIdx.z * AB_TOKENS;
+  const int nt = min(AB_TOKENS, n_tokens - t0);
+  // this warp's rows of Wk_h: weights, fetched (16 in flight) before the wait for the queries
+  const int rows_per = (dk + 3) / 4;
+  const int i0 = warp * rows_per, i1 = min(dk, i0 + rows_per);
+  const T* wk = w_k + (size_t)h * dk * rank + (r < rank ? r : 0);
+  float acc[AB_TOKENS];
+#pragma unroll
+  for (int t = 0; t < AB_TOKENS; ++t) acc[t] = 0.f;
+  pdl_wait();
+  for (int i = threadIdx.x; i < nt * dk; i += 128) {
+    const int t = t0 + i / dk, c = h * dk + i % dk;
+    s_q[i] = q_is_f32 ? reinterpret_cast<const float*>(q)[(size_t)t * ldq + c]
+                      : to_float(reinterpret_cast<const __nv_bfloat16*>(q)[(size_t)t * ldq + c]);
+  }
+  __syncthreads();
+  for (int ib = i0; ib < i1; ib += 16) {
+    float w[16];
+#pragma unroll
+    for (int k = 0; k < 16; ++k) w[k] = (ib + k < i1) ? to_float(wk[(size_t)(ib + k) * rank]) : 0.f;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      if (ib + k < i1) {
+#pragma unroll
+        for (int t = 0; t < AB_TOKENS; ++t) acc[t] = fmaf(s_q[t * dk + ib + k], w[k], acc[t]);   // (rows of absent tokens are unused)
+      }
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < AB_TOKENS; ++t) s_part[(warp * AB_TOKENS + t) * AB_COLS + lane] = acc[t];
+  __syncthreads();
+  // the four warps' sums meet in warp order; warp w writes tokens w, w + 4
+  for (int t = warp; t < nt; t += 4) {
+    float a = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) a += s_part[(w * AB_TOKENS + t) * AB_COLS + lane];
+    if (r < rank) q_lat[((size_t)(t0 + t) * H + h) * rank + r] = a;
+  }
+}
+
+constexpr int LP_WARPS = 4;
+constexpr int LP_UNROLL = 4;
+
+// 16 bytes of a latent row as floats: V = 8 bfloat16 or 4 float
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+  static constexpr int V = 4;
+  __device__ static __forceinline__ void load(const float* p, float* o) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+  }
+};
+template <> struct Vec16<__nv_bfloat16> {
+  static constexpr int V = 8;
+  __device__ static __forceinline__ void load(const __nv_bfloat16* p, float* o) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __bfloat1622float2(h[k]);
+      o[2 * k] = f.x; o[2 * k + 1] = f.y;
+    }
+  }
+};
+
+// parts [T, H, S, rank + 2]: (max, sum, weighted latent) of each slice.  A lane holds CH pieces of 16 bytes of a
+// latent row (rank <= 32 * CH * V, rank a multiple of V); the page numbers and then the rows of LP_UNROLL keys are
+// fetched together before any of them is used.
+template <typename T, int CH>
+__global__ void __launch_bounds__(LP_WARPS * 32)
+latent_partial_kernel(const float* __restrict__ q_lat, const T* __restrict__ pages, const int* __restrict__ page_table,
+                      int max_pages, int page_size, const int* __restrict__ seq_slot,
+                      const int* __restrict__ token_seq, const int* __restrict__ token_pos, float* __restrict__ parts,
+                      int H, int rank, int n_slices, float scale, int window) {
+  constexpr int V = Vec16<T>::V;
+  pdl_launch_dependents();
+  extern __shared__ float s_acc[];                              // [LP_WARPS][rank]
+  __shared__ float s_m[LP_WARPS], s_l[LP_WARPS];
+  const int t = blockIdx.x, h = blockIdx.y, slice = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int pos = token_pos[t];
+  const int* table = page_table + (size_t)seq_slot[token_seq[t]] * max_pages;
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int per = (pos - lo + n_slices) / n_slices;             // keys of a slice (the last may have fewer)
+  const int j0 = lo + slice * per, j1 = min(pos + 1, j0 + per);
+  pdl_wait();
+  const float* ql_g = q_lat + ((size_t)t * H + h) * rank;
+  float ql[CH][V], acc[CH][V];
+#pragma unroll
+  for (int i = 0; i < CH; ++i) {
+    const int r = (i * 32 + lane) * V;
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      ql[i][k] = r < rank ? ql_g[r + k] : 0.f;
+      acc[i][k] = 0.f;
+    }
+  }
+  float m = -INFINITY, l = 0.f;
+  for (int jb = j0 + warp * LP_UNROLL; jb < j1; jb += LP_WARPS * LP_UNROLL) {
+    int page[LP_UNROLL];
+#pragma unroll
+    for (int u = 0; u < LP_UNROLL; ++u) page[u] = (jb + u < j1) ? table[(jb + u) / page_size] : 0;
+    const T* row[LP_UNROLL];
+#pragma unroll
+    for (int u = 0; u < LP_UNROLL; ++u)
+      row[u] = pages + ((size_t)page[u] * page_size + ((jb + u < j1) ? (jb + u) % page_size : 0)) * rank;
+    float cv[LP_UNROLL][CH][V];
+#pragma unroll
+    for (int u = 0; u < LP_UNROLL; ++u)
+#pragma unroll
+      for (int i = 0; i < CH; ++i) {
+        const int r = (i * 32 + lane) * V;
+        if (jb + u < j1 && r < rank) {
+          Vec16<T>::load(row[u] + r, cv[u][i]);
+        } else {
+#pragma unroll
+          for (int k = 0; k < V; ++k) cv[u][i][k] = 0.f;
+        }
+      }
+    float sc[LP_UNROLL];
+#pragma unroll
+    for (int u = 0; u < LP_UNROLL; ++u) {
+      float s = 0.f;
+#pragma unroll
+      for (int i = 0; i < CH; ++i)
+#pragma unroll
+        for (int k = 0; k < V; ++k) s = fmaf(ql[i][k], cv[u][i][k], s);
+      sc[u] = (jb + u < j1) ? warp_sum(s) * scale : -INFINITY;
+    }
+    float m_new = m;
+#pragma unroll
+    for (int u = 0; u < LP_UNROLL; ++u) m_new = fmaxf(m_new, sc[u]);
+    const float corr = expf(m - m_new);                         // (the first key of a group is always there)
+    l *= corr;
+#pragma unroll
+    for (int i = 0; i < CH; ++i)
+#pragma unroll
+      for (int k = 0; k < V; ++k) acc[i][k] *= corr;
+#pragma unroll
+    for (int u = 0; u < LP_UNROLL; ++u) {
+      const float p = expf(sc[u] - m_new);                      // 0 for a key that is not there
+      l += p;
+#pragma unroll
+      for (int i = 0; i < CH; ++i)
+#pragma unroll
+        for (int k = 0; k < V; ++k) acc[i][k] = fmaf(p, cv[u][i][k], acc[i][k]);
+    }
+    m = m_new;
+  }
+  if (lane == 0) { s_m[warp] = m; s_l[warp] = l; }
+#pragma unroll
+  for (int i = 0; i < CH; ++i) {
+    const int r = (i * 32 + lane) * V;
+    if (r < rank) {
+#pragma unroll
+      for (int k = 0; k < V; ++k) s_acc[warp * rank + r + k] = acc[i][k];
+    }
+  }
+  __syncthreads();
+  float M = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < LP_WARPS; ++w) M = fmaxf(M, s_m[w]);
+  float f[LP_WARPS], L = 0.f;
+#pragma unroll
+  for (int w = 0; w < LP_WARPS; ++w) {
+    f[w] = s_m[w] == -INFINITY ? 0.f : expf(s_m[w] - M);
+    L = fmaf(s_l[w], f[w], L);
+  }
+  float* out = parts + (((size_t)t * H + h) * n_slices + slice) * (rank + 2);
+  if (threadIdx.x == 0) { out[0] = M; out[1] = L; }             // an empty slice leaves (-inf, 0, zeros)
+  for (int r = threadIdx.x; r < rank; r += blockDim.x) {
+    float a = 0.f;
+#pragma unroll
+    for (int w = 0; w < LP_WARPS; ++w) a = fmaf(s_acc[w * rank + r], f[w], a);
+    out[2 + r] = a;
+  }
+}
+
+constexpr int LO_COLS = 8;      // value columns of a block of `out` (one warp each)
+constexpr int LO_TOKENS = 8;    // tokens whose weighted latents sit in shared memory at a time
+
+template <typename T, int CH>
+__global__ void __launch_bounds__(LO_COLS * 32)
+latent_out_kernel(const float* __restrict__ parts, const T* __restrict__ w_v, const float* __restrict__ sink,
+                  T* __restrict__ out, int ldo, int n_tokens, int H, int dv, int rank, int n_slices) {
+  constexpr int V = Vec16<T>::V;
+  pdl_launch_dependents();
+  extern __shared__ float s_lat[];                              // [LO_TOKENS][rank]
+  const int h = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int e = blockIdx.y * LO_COLS + warp;
+  // this warp's row of Wv_h: a weight, fetched before the wait
+  float wv[CH][V];
+#pragma unroll
+  for (int i = 0; i < CH; ++i) {
+    const int r = (i * 32 + lane) * V;
+    if (e < dv && r < rank) {
+      Vec16<T>::load(w_v + ((size_t)h * dv + e) * rank + r, wv[i]);
+    } else {
+#pragma unroll
+      for (int k = 0; k < V; ++k) wv[i][k] = 0.f;
+    }
+  }
+  const float sk = sink ? sink[h] : -INFINITY;
+  pdl_wait();
+  for (int t0 = 0; t0 < n_tokens; t0 += LO_TOKENS) {
+    const int nt = min(LO_TOKENS, n_tokens - t0);
+    __syncthreads();
+    for (int tt = warp; tt < nt; tt += LO_COLS) {               // a warp brings a token's slices together
+      const float* p = parts + ((size_t)(t0 + tt) * H + h) * n_slices * (rank + 2);
+      float M = sk;
+      for (int s = 0; s < n_slices; ++s) M = fmaxf(M, p[(size_t)s * (rank + 2)]);
+      float L = sink ? expf(sk - M) : 0.f;
+      for (int s = 0; s < n_slices; ++s) {
+        const float ms = p[(size_t)s * (rank + 2)];
+        L = fmaf(p[(size_t)s * (rank + 2) + 1], ms == -INFINITY ? 0.f : expf(ms - M), L);
+      }
+      const float inv = 1.0f / L;
+      for (int r = lane; r < rank; r += 32) s_lat[tt * rank + r] = 0.f;
+      for (int s = 0; s < n_slices; ++s) {                      // slices in slice order
+        const float ms = p[(size_t)s * (rank + 2)];
+        const float fs = ms == -INFINITY ? 0.f : expf(ms - M) * inv;
+        const float* ps = p + (size_t)s * (rank + 2) + 2;
+        for (int r = lane; r < rank; r += 32) s_lat[tt * rank + r] = fmaf(ps[r], fs, s_lat[tt * rank + r]);
+      }
+    }
+    __syncthreads();
+    if (e < dv) {
+      for (int tt = 0; tt < nt; ++tt) {
+        float a = 0.f;
+#pragma unroll
+        for (int i = 0; i < CH; ++i) {
+          const int r = (i * 32 + lane) * V;
+          if (r < rank) {
+#pragma unroll
+            for (int k = 0; k < V; ++k) a = fmaf(wv[i][k], s_lat[tt * rank + r + k], a);
+          }
+        }
+        a = warp_sum(a);
+        if (lane == 0) out[(size_t)(t0 + tt) * ldo + h * dv + e] = from_float<T>(a);
+      }
+    }
+  }
+}
+
+template <typename T, int CH>
+static int launch_latent_few(const void* q, int q_is_f32, int ldq, const void* w_k, const void* w_v, const float* sink,
+                             const void* pages, const int* page_table, int max_pages, int page_size,
+                             const int* seq_slot, const int* token_seq, const int* token_pos, void* out, int ldo,
+                             int n_tokens, int H, int dk, int dv, int rank, float scale, int window, int n_slices,
+                             float* q_lat, float* parts, cudaStream_t stream) {
+  const size_t smem_a = (size_t)(AB_TOKENS * dk + 4 * AB_TOKENS * AB_COLS) * sizeof(float);
+  const size_t smem_p = (size_t)LP_WARPS * rank * sizeof(float);
+  const size_t smem_o = (size_t)LO_TOKENS * rank * sizeof(float);
+  if (smem_a > 48 * 1024 || smem_p > 48 * 1024 || smem_o > 48 * 1024) return DLGO_ERR_SIZE;
+  launch_kernel(latent_absorb_kernel<T>, dim3(H, (rank + AB_COLS - 1) / AB_COLS, (n_tokens + AB_TOKENS - 1) / AB_TOKENS), dim3(128),
+                smem_a, stream, q, q_is_f32, ldq, (const T*)w_k, q_lat, n_tokens, H, dk, rank);
+  int st = launch_status();
+  if (st != DLGO_OK) return st;
+  launch_kernel(latent_partial_kernel<T, CH>, dim3(n_tokens, H, n_slices), dim3(LP_WARPS * 32), smem_p, stream, q_lat,
+                (const T*)pages, page_table, max_pages, page_size, seq_slot, token_seq, token_pos, parts, H, rank,
+                n_slices, scale, window);
+  st = launch_status();
+  if (st != DLGO_OK) return st;
+  launch_kernel(latent_out_kernel<T, CH>, dim3(H, (dv + LO_COLS - 1) / LO_COLS), dim3(LO_COLS * 32), smem_o, stream,
+                parts, (const T*)w_v, sink, (T*)out, ldo, n_tokens, H, dv, rank, n_slices);
+  return launch_status();
+}
+
 template <typename T, int NP>
 static int launch_latent(const void* q, int q_is_f32, int ldq, const void* w_k, const void* w_v, const float* sink,
                          const void* pages, const int* page_table, int max_pages, int page_size, const int* seq_slot,
@@ -232,10 +533,10 @@ DLGO_EXPORT int dlgo_latent_gather(const void* pages, int dtype, const int* page
   if (n_tmp <= 0) return DLGO_OK;
   if (rank <= 0 || page_size <= 0) return DLGO_ERR_SIZE;
   if (dtype == DLGO_F32)
-    launch_kernel(latent_gather_kernel<float>, dim3(n_tmp), dim3(256), 0, stream, (const float*)pages, page_table,
+    launch_kernel(latent_gather_kernel<float>, dim3(n_tmp, GATHER_PARTS), dim3(256), 0, stream, (const float*)pages, page_table,
                   max_pages, page_size, tmp_pages, seq_slot, (float*)out, rank);
   else if (dtype == DLGO_BF16)
-    launch_kernel(latent_gather_kernel<__nv_bfloat16>, dim3(n_tmp), dim3(256), 0, stream, (const __nv_bfloat16*)pages,
+    launch_kernel(latent_gather_kernel<__nv_bfloat16>, dim3(n_tmp, GATHER_PARTS), dim3(256), 0, stream, (const __nv_bfloat16*)pages,
                   page_table, max_pages, page_size, tmp_pages, seq_slot, (__nv_bfloat16*)out, rank);
   else
     return DLGO_ERR_DTYPE;
@@ -256,6 +557,51 @@ static int latent_by_rank(const void* q, int q_is_f32, int ldq, const void* w_k,
   if (rank <= 512) return launch_latent<T, 8>(LATENT_ARGS);
   if (rank <= 1024) return launch_latent<T, 16>(LATENT_ARGS);
   return DLGO_ERR_SIZE;
+}
+
+#define FEW_ARGS q, q_is_f32, ldq, w_k, w_v, sink, pages, page_table, max_pages, page_size, seq_slot, token_seq, \
+                 token_pos, out, ldo, T_tokens, H, dk, dv, rank, scale, window, n_slices, q_lat, parts, stream
+
+template <typename T>
+static int latent_few_by_rank(const void* q, int q_is_f32, int ldq, const void* w_k, const void* w_v,
+                              const float* sink, const void* pages, const int* page_table, int max_pages,
+                              int page_size, const int* seq_slot, const int* token_seq, const int* token_pos,
+                              void* out, int ldo, int T_tokens, int H, int dk, int dv, int rank, float scale,
+                              int window, int n_slices, float* q_lat, float* parts, cudaStream_t stream) {
+  constexpr int V = 16 / (int)sizeof(T);
+  if (rank % V) return DLGO_ERR_SIZE;                           // rows are read 16 bytes at a time
+  const int lanes = (rank + V - 1) / V;                         // 16-byte pieces of a row
+  if (lanes <= 32) return launch_latent_few<T, 1>(FEW_ARGS);
+  if (lanes <= 64) return launch_latent_few<T, 2>(FEW_ARGS);
+  if (lanes <= 128) return launch_latent_few<T, 4>(FEW_ARGS);
+  if (lanes <= 256) return launch_latent_few<T, 8>(FEW_ARGS);
+  return DLGO_ERR_SIZE;
+}
+
+// The same attention as three launches (see above) for steps of few tokens: q_lat [T, H, rank] and
+// parts [T, H, n_slices, rank + 2] are fp32 scratch; every token's visible keys are cut into n_slices slices.
+// 1 if the three-launch kernels take this rank and type (rows read 16 bytes at a time)
+DLGO_EXPORT int dlgo_latent_attention_few_takes(int dtype, int rank) {
+  const int v = dtype == DLGO_F32 ? 4 : 8;
+  return (dtype == DLGO_F32 || dtype == DLGO_BF16) && rank % v == 0 && rank <= 256 * v;
+}
+
+DLGO_EXPORT int dlgo_latent_attention_few(const void* q, int q_is_f32, int ldq, const void* w_k, const void* w_v,
+                                          const float* sink, const void* pages, int dtype, const int* page_table,
+                                          int max_pages, int page_size, const int* seq_slot, const int* token_seq,
+                                          const int* token_pos, void* out, int ldo, int T_tokens, int H, int dk,
+                                          int dv, int rank, float scale, int window, int n_slices, float* q_lat,
+                                          float* parts, cudaStream_t stream) {
+  if (T_tokens <= 0) return DLGO_OK;
+  if (H <= 0 || dk <= 0 || dv <= 0 || rank <= 0 || (rank & 1) || page_size <= 0 || window < 0 || n_slices < 1 ||
+      n_slices > 65535 || H > 65535)
+    return DLGO_ERR_SIZE;
+  if (((uintptr_t)pages & 15) || ((uintptr_t)w_v & 15)) return DLGO_ERR_ALIGN;
+  if (dtype == DLGO_F32) return latent_few_by_rank<float>(FEW_ARGS);
+  if (dtype == DLGO_BF16) {
+    return latent_few_by_rank<__nv_bfloat16>(FEW_ARGS);
+  }
+  return DLGO_ERR_DTYPE;
 }
 
 // q [T, >= H*dk] (fp32 or the cache's type), w_k [H*dk, rank], w_v [H*dv, rank], pages [n, page_size, rank],

@@ -38,8 +38,17 @@ struct StreamsStep {
   const int* rows;      // [R] rows of X to read (read part only), or null
 };
 
+template <typename TO> __device__ __forceinline__ void store4(TO* o, float a, float b, float c, float d);
+template <> __device__ __forceinline__ void store4<float>(float* o, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(o) = make_float4(a, b, c, d);
+}
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* o, float a, float b, float c, float d) {
+  __nv_bfloat162 h[2] = {__floats2bfloat162_rn(a, b), __floats2bfloat162_rn(c, d)};
+  *reinterpret_cast<uint2*>(o) = *reinterpret_cast<uint2*>(h);
+}
+
 template <typename TO>
-__global__ void streams_step_kernel(StreamsStep p) {
+__global__ void __launch_bounds__(256) streams_step_kernel(StreamsStep p) {
   pdl_launch_dependents();
   __shared__ float s_mix[MAX_STREAMS * MAX_STREAMS], s_wout[MAX_STREAMS], s_coeff[MAX_STREAMS];
   __shared__ float scratch[32];
@@ -60,40 +69,81 @@ __global__ void streams_step_kernel(StreamsStep p) {
   float* yr = p.y ? p.y + (size_t)row * d : nullptr;
   TO* o = p.out ? reinterpret_cast<TO*>(p.out) + (size_t)r * d : nullptr;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) {
-    float x[MAX_STREAMS];
+  // four columns per thread and trip (16-byte accesses) where the row length allows, else one
+  const int W = (d & 3) == 0 ? 4 : 1;
+  for (int i0 = threadIdx.x * W; i0 < d; i0 += blockDim.x * W) {
+    float x[MAX_STREAMS][4];
 #pragma unroll
-    for (int a = 0; a < MAX_STREAMS; ++a) x[a] = a < s ? xr[(size_t)a * d + i] : 0.f;
+    for (int a = 0; a < MAX_STREAMS; ++a) {
+      if (a < s) {
+        if (W == 4) {
+          const float4 v = *reinterpret_cast<const float4*>(xr + (size_t)a * d + i0);
+          x[a][0] = v.x; x[a][1] = v.y; x[a][2] = v.z; x[a][3] = v.w;
+        } else {
+          x[a][0] = xr[(size_t)a * d + i0];
+          x[a][1] = x[a][2] = x[a][3] = 0.f;
+        }
+      }
+    }
     if (yr) {
-      float yv = yr[i];
-      if (p.y_bias) yv += p.y_bias[i];
-      if (p.clear_y) yr[i] = 0.f;
-      float nx[MAX_STREAMS];
+      float yv[4] = {0.f, 0.f, 0.f, 0.f};
+      if (W == 4) {
+        const float4 v = *reinterpret_cast<const float4*>(yr + i0);
+        yv[0] = v.x; yv[1] = v.y; yv[2] = v.z; yv[3] = v.w;
+        if (p.y_bias) {
+          const float4 b = *reinterpret_cast<const float4*>(p.y_bias + i0);
+          yv[0] += b.x; yv[1] += b.y; yv[2] += b.z; yv[3] += b.w;
+        }
+        if (p.clear_y) *reinterpret_cast<float4*>(yr + i0) = make_float4(0.f, 0.f, 0.f, 0.f);
+      } else {
+        yv[0] = yr[i0] + (p.y_bias ? p.y_bias[i0] : 0.f);
+        if (p.clear_y) yr[i0] = 0.f;
+      }
+      float nx[MAX_STREAMS][4];
 #pragma unroll
       for (int q = 0; q < MAX_STREAMS; ++q) {
         if (q < s) {
-          float acc = 0.f;
 #pragma unroll
-          for (int a = 0; a < MAX_STREAMS; ++a)
-            if (a < s) acc = fmaf(s_mix[a * s + q], x[a], acc);
-          nx[q] = fmaf(s_wout[q], yv, acc);
-          xr[(size_t)q * d + i] = nx[q];
+          for (int c = 0; c < 4; ++c) {
+            float acc = 0.f;
+#pragma unroll
+            for (int a = 0; a < MAX_STREAMS; ++a)
+              if (a < s) acc = fmaf(s_mix[a * s + q], x[a][c], acc);
+            nx[q][c] = fmaf(s_wout[q], yv[c], acc);
+          }
+          if (W == 4)
+            *reinterpret_cast<float4*>(xr + (size_t)q * d + i0) = make_float4(nx[q][0], nx[q][1], nx[q][2], nx[q][3]);
+          else
+            xr[(size_t)q * d + i0] = nx[q][0];
         }
       }
 #pragma unroll
-      for (int q = 0; q < MAX_STREAMS; ++q) x[q] = q < s ? nx[q] : 0.f;
+      for (int q = 0; q < MAX_STREAMS; ++q)
+        if (q < s) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) x[q][c] = nx[q][c];
+        }
     }
     if (o) {
-      float u = 0.f;
+      float u[4];
 #pragma unroll
-      for (int a = 0; a < MAX_STREAMS; ++a)
-        if (a < s) u = fmaf(s_coeff[a], x[a], u);
-      if (p.norm_kind == NORM_DYT) {
-        o[i] = from_float<TO>(fmaf(tanhf(alpha * u), p.nw[i], p.nb ? p.nb[i] : 0.f));
-      } else if (p.norm_kind == NORM_RMS) {
-        ss = fmaf(u, u, ss);
+      for (int c = 0; c < 4; ++c) {
+        u[c] = 0.f;
+#pragma unroll
+        for (int a = 0; a < MAX_STREAMS; ++a)
+          if (a < s) u[c] = fmaf(s_coeff[a], x[a][c], u[c]);
+      }
+      if (p.norm_kind == NORM_RMS) {
+        for (int c = 0; c < W; ++c) ss = fmaf(u[c], u[c], ss);
       } else {
-        o[i] = from_float<TO>(u);
+        float r4[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int i = i0 + (c < W ? c : 0);
+          r4[c] = p.norm_kind == NORM_DYT ? fmaf(tanhf(alpha * u[c]), p.nw[i], p.nb ? p.nb[i] : 0.f) : u[c];
+        }
+        if (W == 4) store4<TO>(o + i0, r4[0], r4[1], r4[2], r4[3]);
+        else o[i0] = from_float<TO>(r4[0]);
       }
     }
   }
@@ -125,6 +175,21 @@ __global__ void bias_act_kernel(const float* z, int ldz, const float* __restrict
                                 int act) {
   pdl_launch_dependents();
   pdl_wait();
+  if ((n & 3) == 0 && (ldz & 3) == 0 && (ldo & 3) == 0 && ((uintptr_t)z & 15) == 0 && ((uintptr_t)out & 15) == 0 &&
+      (bias == nullptr || ((uintptr_t)bias & 15) == 0)) {
+    const int n4 = n >> 2;
+    const size_t total4 = (size_t)T * n4;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total4; e += (size_t)gridDim.x * blockDim.x) {
+      const int t = (int)(e / n4), i = (int)(e % n4) * 4;
+      float4 v = *reinterpret_cast<const float4*>(z + (size_t)t * ldz + i);
+      if (bias) {
+        const float4 b = __ldg(reinterpret_cast<const float4*>(bias + i));
+        v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+      }
+      store4<TO>(out + (size_t)t * ldo + i, activate(v.x, act), activate(v.y, act), activate(v.z, act), activate(v.w, act));
+    }
+    return;
+  }
   const size_t total = (size_t)T * n;
   for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
     const int t = (int)(e / n), i = (int)(e % n);
@@ -169,7 +234,7 @@ DLGO_EXPORT int dlgo_streams_step(float* X, int T, int s, int d, float* y, const
   if (out && out_dtype != DLGO_F32 && out_dtype != DLGO_BF16) return DLGO_ERR_DTYPE;
   if (out && norm_kind != NORM_NONE && !nw) return DLGO_ERR_SIZE;
   StreamsStep p{X, s, d, y, y_bias, mix, wout, clear_y, coeff, norm_kind, nw, nb, nalpha, eps, out, rows};
-  const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
+  const int threads = d >= 1024 ? 256 : 128;      // (four columns per thread and trip)
   if (out && out_dtype == DLGO_BF16)
     launch_kernel(streams_step_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, p);
   else
@@ -181,7 +246,7 @@ DLGO_EXPORT int dlgo_bias_act(const float* z, int ldz, const float* bias, void* 
                               int n, int act, cudaStream_t stream) {
   if (T <= 0 || n <= 0) return DLGO_OK;
   if (act < ACT_NONE || act > ACT_GELU_TANH) return DLGO_ERR_SIZE;
-  const size_t total = (size_t)T * n;
+  const size_t total = ((size_t)T * n + 3) / 4;
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   if (out_dtype == DLGO_F32)

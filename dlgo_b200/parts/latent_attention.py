@@ -35,6 +35,10 @@ _NAMES = {"q": "q_proj.weight", "q_down": "q_a_proj.weight", "q_norm": "q_a_norm
 PROMPT_TC_MIN_TOKENS = int(os.environ.get("DLGO_LATENT_TC_MIN_TOKENS", 64))
 
 
+FEW_TOKENS = 64      # steps of up to this many tokens run the three-launch kernels
+SLICE_BLOCKS_PER_SM = int(os.environ.get("DLGO_LATENT_SLICE_BLOCKS", 4))   # blocks of the softmax launch wanted per SM
+
+
 class LatentAttention(Mixer):
     def __init__(self, hidden_size: int, num_heads: int, qk_dim: int, v_dim: int, kv_rank: int, scale: float,
                  eps: float, q_rank: Optional[int] = None, window: Optional[int] = None, sink: bool = False,
@@ -117,6 +121,20 @@ class LatentAttention(Mixer):
         q = self.w_q_up(cq, STORE) if self.q_rank is not None else proj[:, :n_q]
         if self.prompt_on_tensor_cores(ctx, cache):
             out = self._prompt_tc(q, ctx, cache)
+            self.wo(out, ADD_F32, residual)
+            return
+        T, H, R = ctx.n_tokens, self.n_heads, self.kv_rank
+        if T <= FEW_TOKENS and K.latent_attention_few_takes(cache.keys.dtype, R):
+            # decoding: enough blocks for the whole GPU whatever the batch (a token's keys in slices of 64 or more)
+            longest = ctx.capacity if ctx.captured else ctx.max_len
+            span = min(longest, self.window) if self.window else longest
+            from .tensor_core import sm_count
+            n_slices = max(1, min((SLICE_BLOCKS_PER_SM * sm_count(x.device)) // (T * H), span // 32, 32))
+            out = K.latent_attention_few(q, self.w_k_up, self.w_v_up, self.sink, cache.keys, cache.page_table,
+                                         ctx.seq_slot, ctx.token_seq, ctx.token_pos, H, self.qk_dim, self.v_dim,
+                                         self.scale, self.window or 0, n_slices,
+                                         ctx.scratch("latent_q", T * H * R),
+                                         ctx.scratch("latent_parts", T * H * n_slices * (R + 2)))
             self.wo(out, ADD_F32, residual)
             return
         out = K.latent_attention(q, self.w_k_up, self.w_v_up, self.sink, cache.keys, cache.page_table, ctx.seq_slot,
