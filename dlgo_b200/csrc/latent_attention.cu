@@ -87,6 +87,13 @@ __device__ __forceinline__ float2 load_pair(const __nv_bfloat16* p) {
   return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
 }
 
+// a pair of neighbouring elements; `vec`: the pair is 2-element aligned and wholly inside the row
+template <typename T>
+__device__ __forceinline__ float2 load_pair_any(const T* row, int r, int rank, bool vec) {
+  if (vec) return load_pair(row + r);
+  return make_float2(to_float(row[r]), r + 1 < rank ? to_float(row[r + 1]) : 0.f);
+}
+
 constexpr int LA_WARPS = 8;
 
 // NP: pairs of latent dimensions a lane holds (rank <= 64 * NP, rank even)
@@ -110,6 +117,7 @@ latent_attention_kernel(const void* __restrict__ q, int q_is_f32, int ldq, const
   const int slot = seq_slot[token_seq[t]];
   const int* table = page_table + (size_t)slot * max_pages;
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const bool vec = (rank & 1) == 0;          // rows start on a pair's boundary (the bases are 16-byte aligned)
   pdl_wait();
   for (int i = threadIdx.x; i < dk; i += blockDim.x)
     s_q[i] = q_is_f32 ? reinterpret_cast<const float*>(q)[(size_t)t * ldq + h * dk + i]
@@ -127,7 +135,7 @@ latent_attention_kernel(const void* __restrict__ q, int q_is_f32, int ldq, const
 #pragma unroll
   for (int i = 0; i < NP; ++i) {
     const int r = (i * 32 + lane) * 2;
-    ql[i] = r < rank ? make_float2(s_lat[r], s_lat[r + 1]) : make_float2(0.f, 0.f);
+    ql[i] = r < rank ? make_float2(s_lat[r], r + 1 < rank ? s_lat[r + 1] : 0.f) : make_float2(0.f, 0.f);
     acc[i] = make_float2(0.f, 0.f);
   }
   float m = -INFINITY, l = 0.f;
@@ -139,7 +147,7 @@ latent_attention_kernel(const void* __restrict__ q, int q_is_f32, int ldq, const
 #pragma unroll
     for (int i = 0; i < NP; ++i) {
       const int r = (i * 32 + lane) * 2;
-      cv[i] = r < rank ? load_pair(c + r) : make_float2(0.f, 0.f);
+      cv[i] = r < rank ? load_pair_any(c, r, rank, vec) : make_float2(0.f, 0.f);
       s = fmaf(ql[i].x, cv[i].x, s);
       s = fmaf(ql[i].y, cv[i].y, s);
     }
@@ -159,7 +167,8 @@ latent_attention_kernel(const void* __restrict__ q, int q_is_f32, int ldq, const
 #pragma unroll
   for (int i = 0; i < NP; ++i) {
     const int r = (i * 32 + lane) * 2;
-    if (r < rank) { s_acc[warp * rank + r] = acc[i].x; s_acc[warp * rank + r + 1] = acc[i].y; }
+    if (r < rank) s_acc[warp * rank + r] = acc[i].x;
+    if (r + 1 < rank) s_acc[warp * rank + r + 1] = acc[i].y;
   }
   __syncthreads();
   // the warps' parts meet in warp order; the sink joins the denominator only
@@ -187,9 +196,9 @@ latent_attention_kernel(const void* __restrict__ q, int q_is_f32, int ldq, const
     const T* row = wv + (size_t)e * rank;
     float a = 0.f;
     for (int r = lane * 2; r < rank; r += 64) {
-      const float2 wv2 = load_pair(row + r);
+      const float2 wv2 = load_pair_any(row, r, rank, vec);
       a = fmaf(wv2.x, s_lat[r], a);
-      a = fmaf(wv2.y, s_lat[r + 1], a);
+      if (r + 1 < rank) a = fmaf(wv2.y, s_lat[r + 1], a);
     }
     a = warp_sum(a);
     if (lane == 0) out[(size_t)t * ldo + h * dv + e] = from_float<T>(a);
@@ -593,7 +602,7 @@ DLGO_EXPORT int dlgo_latent_attention_few(const void* q, int q_is_f32, int ldq, 
                                           int dv, int rank, float scale, int window, int n_slices, float* q_lat,
                                           float* parts, cudaStream_t stream) {
   if (T_tokens <= 0) return DLGO_OK;
-  if (H <= 0 || dk <= 0 || dv <= 0 || rank <= 0 || (rank & 1) || page_size <= 0 || window < 0 || n_slices < 1 ||
+  if (H <= 0 || dk <= 0 || dv <= 0 || rank <= 0 || page_size <= 0 || window < 0 || n_slices < 1 ||
       n_slices > 65535 || H > 65535)
     return DLGO_ERR_SIZE;
   if (((uintptr_t)pages & 15) || ((uintptr_t)w_v & 15)) return DLGO_ERR_ALIGN;
@@ -612,10 +621,10 @@ DLGO_EXPORT int dlgo_latent_attention(const void* q, int q_is_f32, int ldq, cons
                                       const int* token_pos, void* out, int ldo, int T_tokens, int H, int dk, int dv,
                                       int rank, float scale, int window, cudaStream_t stream) {
   if (T_tokens <= 0) return DLGO_OK;
-  if (H <= 0 || dk <= 0 || dv <= 0 || rank <= 0 || (rank & 1) || page_size <= 0 || window < 0) return DLGO_ERR_SIZE;
+  if (H <= 0 || dk <= 0 || dv <= 0 || rank <= 0 || page_size <= 0 || window < 0) return DLGO_ERR_SIZE;
+  if (((uintptr_t)pages & 7) || ((uintptr_t)w_v & 7)) return DLGO_ERR_ALIGN;
   if (dtype == DLGO_F32) return latent_by_rank<float>(LATENT_ARGS);
   if (dtype == DLGO_BF16) {
-    if (((uintptr_t)pages & 3) || ((uintptr_t)w_v & 3)) return DLGO_ERR_ALIGN;
     return latent_by_rank<__nv_bfloat16>(LATENT_ARGS);
   }
   return DLGO_ERR_DTYPE;

@@ -46,8 +46,8 @@ class LatentAttention(Mixer):
         super().__init__(hidden_size=hidden_size, num_heads=num_heads, qk_dim=qk_dim, v_dim=v_dim, kv_rank=kv_rank,
                          scale=scale, eps=eps, q_rank=q_rank, window=window, sink=sink, cache_group=cache_group,
                          names=names)
-        if kv_rank % 2 or kv_rank > 1024:
-            raise ValueError(f"kv_rank must be even and at most 1024, got {kv_rank}")
+        if not 0 < kv_rank <= 1024:
+            raise ValueError(f"kv_rank must be 1 to 1024, got {kv_rank}")
         if window is not None and window <= 0:
             raise ValueError(f"window must be positive or None, got {window}")
         self.hidden_size, self.n_heads = int(hidden_size), int(num_heads)

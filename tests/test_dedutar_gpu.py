@@ -287,6 +287,28 @@ def test_latent_prompts_on_the_tensor_cores(kind, window, dim):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rank", [21, 18, 72, 264])
+def test_latent_ranks_of_any_size(rank, dtype):
+    """Ranks that are odd, even but no multiple of a 16-byte piece, and beyond one piece per lane: prompt,
+    portions and decoding agree with the plain implementation."""
+    layer = {"type": "latent_attention", "mixer": {"heads": 2, "dim": 12, "vdim": 20, "kv_rank": rank, "q_rank": 9,
+                                                   "scale": 0.3, "mask": {"size": 50}}}
+    cfg = one_layer(layer, streams=1, width=40)
+    w = make_weights(cfg, 10, sharpen=2.0)
+    tokens = random_tokens(90, cfg["vocab"], 6)
+    ref = plain_of(cfg, w, tokens)
+    eng = engine_of(cfg, w, dtype)
+    assert_rows(run_whole(eng, tokens), ref, dtype, "whole")
+    s = eng.take_slot()
+    got = [eng.step([s], [tokens[:70]], [list(range(70))]).clone()]
+    got.append(eng.step([s], [tokens[70:75]], [list(range(5))]).clone())
+    for p in range(75, 90):
+        got.append(eng.step([s], [tokens[p:p + 1]]).clone())
+    eng.free_slot(s)
+    assert_rows(torch.cat(got), ref, dtype, "prompt, a portion, decoding")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_sink_counts_once_and_unscaled(dtype):
     layer = {"type": "latent_attention_2", "mixer": {"heads": 4, "dim": 8, "vdim": 8, "kv_rank": 16, "scale": 0.5}}
     cfg = one_layer(layer, streams=3)
