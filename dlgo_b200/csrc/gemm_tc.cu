@@ -36,7 +36,9 @@ namespace dlgo {
 
 using namespace sm100;
 
-enum { TC_STORE = 0, TC_STORE_F32 = 1, TC_ADD_F32 = 2, TC_SWIGLU = 3, TC_PARTIAL = 4, TC_RED_F32 = 5, TC_ROPE_QKV = 6 };
+enum { TC_STORE = 0, TC_STORE_F32 = 1, TC_ADD_F32 = 2, TC_SWIGLU = 3, TC_PARTIAL = 4, TC_RED_F32 = 5, TC_ROPE_QKV = 6,
+       TC_BIAS_ACT = 7 };   // 7: bf16 act(acc + bias[feature]), bias and activation in fp32 on the accumulator
+enum { TC_ACT_NONE = 0, TC_ACT_RELU2 = 1, TC_ACT_SILU = 2, TC_ACT_GELU_TANH = 3 };
 
 constexpr int TILE_M = 128;
 constexpr int TILE_K = 64;  // 128 bytes of bf16: one swizzle row
@@ -74,6 +76,8 @@ struct TcParams {
   int stages;         // shared-memory ring size
   int staged;         // many-token kernels: epilogue through shared memory and TMA stores
   int static_operand; // 0: none; 1: A, 2: B holds weights no earlier kernel writes (loaded before pdl_wait)
+  const float* bias;  // TC_BIAS_ACT: one number per weight row (feature), or null
+  int act;            // TC_BIAS_ACT: TC_ACT_*
 };
 
 template <int BN> struct TcConfig {
@@ -98,10 +102,56 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
   return g * u * r;
 }
 
-// One row's 32 consecutive columns (or 16 when NV == 16) -> memory, per epilogue.
+template <int ACT> __device__ __forceinline__ float act_value(float z) {
+  if (ACT == TC_ACT_RELU2) { const float r = fmaxf(z, 0.f); return r * r; }
+  if (ACT == TC_ACT_SILU) return z / (1.0f + __expf(-z));
+  if (ACT == TC_ACT_GELU_TANH) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  return z;
+}
+// n accumulator values + bias (b: per value, or one number when `same`) through the activation, in place;
+// the activation is chosen once, outside the loop
+template <int N, int ACT>
+__device__ __forceinline__ void bias_act_run(float* v, const float* b, bool same) {
+#pragma unroll
+  for (int j = 0; j < N; ++j) v[j] = act_value<ACT>(v[j] + (same ? b[0] : b[j]));
+}
+template <int N>
+__device__ __forceinline__ void bias_act_apply(float* v, const float* b, bool same, int act) {
+  switch (act) {
+    case TC_ACT_RELU2: bias_act_run<N, TC_ACT_RELU2>(v, b, same); break;
+    case TC_ACT_SILU: bias_act_run<N, TC_ACT_SILU>(v, b, same); break;
+    case TC_ACT_GELU_TANH: bias_act_run<N, TC_ACT_GELU_TANH>(v, b, same); break;
+    default: bias_act_run<N, TC_ACT_NONE>(v, b, same); break;
+  }
+}
+
+// One row's 32 consecutive columns (or 16 when NV == 16) -> memory, per epilogue `epi`.
+template <int NV>
+__device__ __forceinline__ void epilogue_store_as(const TcParams& p, const float* v, int row, int col0, int lane, int epi);
+
 template <int NV>
 __device__ __forceinline__ void epilogue_store(const TcParams& p, const float* v, int row, int col0, int lane) {
-  if (p.epilogue == TC_SWIGLU) {
+  if (p.epilogue == TC_BIAS_ACT) {
+    // the weight's rows are the features: tile rows when transposed, tile columns otherwise
+    float w[NV], b[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) w[j] = v[j];
+    if (p.transposed) {
+      b[0] = (p.bias != nullptr && row < p.Ra) ? __ldg(p.bias + row) : 0.f;
+    } else {
+#pragma unroll
+      for (int j = 0; j < NV; ++j) b[j] = (p.bias != nullptr && col0 + j < p.Rb) ? __ldg(p.bias + col0 + j) : 0.f;
+    }
+    bias_act_apply<NV>(w, b, p.transposed != 0, p.act);
+    epilogue_store_as<NV>(p, w, row, col0, lane, TC_STORE);
+    return;
+  }
+  epilogue_store_as<NV>(p, v, row, col0, lane, p.epilogue);
+}
+
+template <int NV>
+__device__ __forceinline__ void epilogue_store_as(const TcParams& p, const float* v, int row, int col0, int lane, int epi) {
+  if (epi == TC_SWIGLU) {
     if (!p.transposed) {
       // columns are weight rows: [16 gate | 16 up] per 32 columns -> 16 outputs at column col0 / 2
       static_assert(NV == 32 || NV == 16, "");
@@ -135,7 +185,7 @@ __device__ __forceinline__ void epilogue_store(const TcParams& p, const float* v
     const size_t base = (size_t)row * p.ldo + col0;
     if (col0 + NV <= p.Rb && (p.ldo & 7) == 0) {
       // whole, aligned run of columns: 16-byte accesses
-      if (p.epilogue == TC_STORE) {
+      if (epi == TC_STORE) {
         uint4* o = reinterpret_cast<uint4*>((__nv_bfloat16*)p.out + base);
 #pragma unroll
         for (int j = 0; j < NV / 8; ++j) {
@@ -149,7 +199,7 @@ __device__ __forceinline__ void epilogue_store(const TcParams& p, const float* v
 #pragma unroll
         for (int j = 0; j < NV / 4; ++j) {
           float4 x = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-          if (p.epilogue == TC_ADD_F32) {
+          if (epi == TC_ADD_F32) {
             const float4 y = o[j];
             x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
           }
@@ -161,8 +211,8 @@ __device__ __forceinline__ void epilogue_store(const TcParams& p, const float* v
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
       if (col0 + j < p.Rb) {
-        if (p.epilogue == TC_STORE) ((__nv_bfloat16*)p.out)[base + j] = __float2bfloat16_rn(v[j]);
-        else if (p.epilogue == TC_STORE_F32) ((float*)p.out)[base + j] = v[j];
+        if (epi == TC_STORE) ((__nv_bfloat16*)p.out)[base + j] = __float2bfloat16_rn(v[j]);
+        else if (epi == TC_STORE_F32) ((float*)p.out)[base + j] = v[j];
         else ((float*)p.out)[base + j] += v[j];
       }
     }
@@ -173,8 +223,8 @@ __device__ __forceinline__ void epilogue_store(const TcParams& p, const float* v
       const int col = col0 + j;
       if (col < p.Rb) {
         const size_t o = (size_t)col * p.ldo + row;
-        if (p.epilogue == TC_STORE) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v[j]);
-        else if (p.epilogue == TC_STORE_F32) ((float*)p.out)[o] = v[j];
+        if (epi == TC_STORE) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v[j]);
+        else if (epi == TC_STORE_F32) ((float*)p.out)[o] = v[j];
         else ((float*)p.out)[o] += v[j];
       }
     }
@@ -648,19 +698,41 @@ __device__ __forceinline__ void staged_epilogue(const TcParams& p, const CUtenso
     return;
   }
   // accumulator columns that make one 128-byte output row chunk
-  const int step = p.epilogue == TC_STORE ? 64 : (p.epilogue == TC_SWIGLU ? 128 : 32);
+  const bool bf16_rows = p.epilogue == TC_STORE || p.epilogue == TC_BIAS_ACT;
+  const int step = bf16_rows ? 64 : (p.epilogue == TC_SWIGLU ? 128 : 32);
 #pragma unroll 1
   for (int c0 = 0; c0 < BN; c0 += step, ++chunk) {
     uint8_t* buf = staging + (chunk & 1) * 16384;
     if (issuer) tma_store_wait_read<1>();     // the store that last used this buffer has read it
     asm volatile("bar.sync 1, 128;" ::: "memory");
     uint8_t* row = buf + r * 128;
-    if (p.epilogue == TC_STORE) {
+    if (bf16_rows) {
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         float v[32];
         tmem_ld_32x32(lane_addr + c0 + 32 * h, v);
         tmem_ld_wait();
+        if (p.epilogue == TC_BIAS_ACT) {
+          // (not transposed: columns are the weight's rows; every row of the tile adds the same 32 numbers,
+          // fetched 16 bytes at a time where the run is whole and aligned)
+          const int f0 = col0 + c0 + 32 * h;
+          const bool whole = p.bias != nullptr && f0 + 32 <= p.Rb && ((uintptr_t)(p.bias + f0) & 15) == 0;
+          float b[32];
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (whole) {
+              q = __ldg(reinterpret_cast<const float4*>(p.bias + f0 + j));
+            } else if (p.bias != nullptr) {
+              if (f0 + j < p.Rb) q.x = __ldg(p.bias + f0 + j);
+              if (f0 + j + 1 < p.Rb) q.y = __ldg(p.bias + f0 + j + 1);
+              if (f0 + j + 2 < p.Rb) q.z = __ldg(p.bias + f0 + j + 2);
+              if (f0 + j + 3 < p.Rb) q.w = __ldg(p.bias + f0 + j + 3);
+            }
+            b[j] = q.x; b[j + 1] = q.y; b[j + 2] = q.z; b[j + 3] = q.w;
+          }
+          bias_act_apply<32>(v, b, false, p.act);
+        }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           __nv_bfloat162 b2[4];
@@ -1048,7 +1120,8 @@ int make_map(CUtensorMap* m, const void* base, int rows, int K, int ld, int box_
 int make_out_map(CUtensorMap* m, const TcParams& p) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return DLGO_ERR_DRIVER;
-  const bool bf16 = p.epilogue == TC_STORE || p.epilogue == TC_SWIGLU || p.epilogue == TC_ROPE_QKV;
+  const bool bf16 = p.epilogue == TC_STORE || p.epilogue == TC_SWIGLU || p.epilogue == TC_ROPE_QKV ||
+                    p.epilogue == TC_BIAS_ACT;
   const int esize = bf16 ? 2 : 4;
   const long long cols = p.epilogue == TC_SWIGLU ? p.Rb / 2 : p.Rb;
   if (((uintptr_t)p.out & 15) != 0 || ((long long)p.ldo * esize) % 16 != 0) return DLGO_ERR_ALIGN;
@@ -1217,12 +1290,34 @@ DLGO_EXPORT int dlgo_gemm_tc_tiles(int Ra, int Rb, int bn) {
 // tiles are then requested before the kernel waits for its predecessor), else 0.
 // pair_tile: 0, or 128 / 256 to compute 256 x pair_tile tiles with pairs of CTAs (cta_group::2; many
 // tokens only: not transposed, one K-slice; bn is then ignored).
+static int gemm_tc_impl(const void* A, int Ra, int lda, const void* B, int Rb, int ldb, int K, void* out, int ldo,
+                        int transposed, int epilogue, int bn, int splits, float* workspace, int* counters,
+                        int static_operand, int pair_tile, const float* bias, int act, cudaStream_t stream);
+
 DLGO_EXPORT int dlgo_gemm_tc(const void* A, int Ra, int lda, const void* B, int Rb, int ldb, int K, void* out,
                              int ldo, int transposed, int epilogue, int bn, int splits, float* workspace,
                              int* counters, int static_operand, int pair_tile, cudaStream_t stream) {
+  if (epilogue < 0 || epilogue > 5) return DLGO_ERR_SIZE;
+  return gemm_tc_impl(A, Ra, lda, B, Rb, ldb, K, out, ldo, transposed, epilogue, bn, splits, workspace, counters,
+                      static_operand, pair_tile, nullptr, 0, stream);
+}
+
+// The same product with epilogue 7: out (bf16) = act(acc + bias[feature]) with bias (fp32, one per weight row, or
+// null) and activation (0 none, 1 relu squared, 2 silu, 3 tanh-form gelu) applied in fp32 on the accumulator.
+DLGO_EXPORT int dlgo_gemm_tc_bias_act(const void* A, int Ra, int lda, const void* B, int Rb, int ldb, int K, void* out,
+                                      int ldo, int transposed, int bn, int splits, float* workspace, int* counters,
+                                      int static_operand, int pair_tile, const float* bias, int act,
+                                      cudaStream_t stream) {
+  if (act < TC_ACT_NONE || act > TC_ACT_GELU_TANH) return DLGO_ERR_SIZE;
+  return gemm_tc_impl(A, Ra, lda, B, Rb, ldb, K, out, ldo, transposed, TC_BIAS_ACT, bn, splits, workspace, counters,
+                      static_operand, pair_tile, bias, act, stream);
+}
+
+static int gemm_tc_impl(const void* A, int Ra, int lda, const void* B, int Rb, int ldb, int K, void* out, int ldo,
+                        int transposed, int epilogue, int bn, int splits, float* workspace, int* counters,
+                        int static_operand, int pair_tile, const float* bias, int act, cudaStream_t stream) {
   if (Ra <= 0 || Rb <= 0) return DLGO_OK;
   if (K <= 0 || K % 8 || lda < K || ldb < K || splits < 1) return DLGO_ERR_SIZE;
-  if (epilogue < 0 || epilogue > 5) return DLGO_ERR_SIZE;
   if (splits > (K + TILE_K - 1) / TILE_K) return DLGO_ERR_SIZE;
   if ((epilogue == TC_PARTIAL || epilogue == TC_RED_F32) && !transposed) return DLGO_ERR_SIZE;
   if (splits > 1 && epilogue != TC_PARTIAL && epilogue != TC_RED_F32 &&
@@ -1241,6 +1336,8 @@ DLGO_EXPORT int dlgo_gemm_tc(const void* A, int Ra, int lda, const void* B, int 
   p.Ra = Ra; p.Rb = Rb; p.K = K; p.out = out; p.ldo = ldo; p.transposed = transposed; p.epilogue = epilogue;
   p.splits = splits; p.workspace = workspace; p.counters = counters;
   p.static_operand = (static_operand == 1 || static_operand == 2) ? static_operand : 0;
+  p.bias = bias;
+  p.act = act;
   if (!transposed && splits == 1 && pair_tile != 0) {
     // many tokens, CTA pairs: A's box is 128 rows, B's box is half the tile's width
     if (pair_tile != 128 && pair_tile != 256) return DLGO_ERR_SIZE;

@@ -759,6 +759,39 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, transposed: boo
     return out
 
 
+def gemm_tc_bias_act(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, transposed: bool, bn: int,
+                     bias: Optional[torch.Tensor], act: int, splits: int = 1, workspace: Optional[torch.Tensor] = None,
+                     counters: Optional[torch.Tensor] = None, static_operand: int = 0, pair_tile: int = 0) -> torch.Tensor:
+    """:func:`gemm_tc` whose epilogue writes ``act(D + bias)`` as bfloat16: ``bias`` (fp32, one number per row of
+    the weight operand, or None) and the activation (``ACT_*``) are applied in fp32 on the accumulator.  The
+    weight is ``a`` when ``transposed`` (few tokens) and ``b`` otherwise."""
+    for n, t in (("a", a), ("b", b)):
+        if not t.is_cuda or t.dtype != torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1:
+            raise KernelError(f"gemm_tc_bias_act: {n} must be a 2-D bfloat16 GPU tensor with unit inner stride")
+    ra, k = a.shape
+    rb, k2 = b.shape
+    if k != k2:
+        raise KernelError(f"gemm_tc_bias_act: a has K={k}, b has K={k2}")
+    want_shape = (rb, ra) if transposed else (ra, rb)
+    if out.dtype != torch.bfloat16 or out.dim() != 2 or tuple(out.shape) != want_shape or out.stride(1) != 1:
+        raise KernelError(f"gemm_tc_bias_act: out must be bfloat16 {list(want_shape)} with unit inner stride")
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+        if bias.numel() != (ra if transposed else rb):
+            raise KernelError("gemm_tc_bias_act: one bias per row of the weight")
+    if splits > 1:
+        need = gemm_tc_workspace_floats(ra, rb, bn, splits)
+        tiles = ((ra + TC_TILE_M - 1) // TC_TILE_M) * ((rb + bn - 1) // bn)
+        if workspace is None or workspace.numel() < need or counters is None or counters.numel() < tiles:
+            raise KernelError(f"gemm_tc_bias_act: {splits} K-slices need {need} floats of workspace and {tiles} counters")
+    st = _lib("gemm_tc").dlgo_gemm_tc_bias_act(
+        _ptr(a), _i(ra), _i(a.stride(0)), _ptr(b), _i(rb), _i(b.stride(0)), _i(k), _ptr(out), _i(out.stride(0)),
+        _i(1 if transposed else 0), _i(bn), _i(splits), _ptr(workspace), _ptr(counters), _i(static_operand),
+        _i(pair_tile), _ptr(bias), _i(act), _stream())
+    _check(st, "gemm_tc_bias_act")
+    return out
+
+
 class RopeArgs(ctypes.Structure):
     """What the q|k|v projection's epilogue needs to rotate q and k and to append k and v (DlgoRopeArgs)."""
     _fields_ = [("cos_t", _p), ("sin_t", _p), ("token_pos", _p), ("token_seq", _p), ("seq_slot", _p),

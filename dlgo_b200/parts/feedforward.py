@@ -7,6 +7,7 @@ experts, no routing.
 """
 from __future__ import annotations
 
+import os
 from typing import Any, Callable, Dict, Mapping, Optional
 
 import torch
@@ -59,10 +60,14 @@ class SwiGLU(FeedForward):
             self.w_down(h, ADD_F32, residual)
 
 
+_FUSED_BIAS_ACT = os.environ.get("DLGO_FUSED_BIAS_ACT", "1") != "0"
+
+
 class ReluSquaredMLP(FeedForward):
     """Dense two-matrix feed-forward with the square of relu between: ``y = Wd . relu(Wu . x + bu)^2 + bd``
     (``bias`` False: no bu, bd).  ``names``: tensor names below the part's prefix.  Bias and activation run in
-    fp32 on the contraction's fp32 result."""
+    fp32 on the contraction's accumulator (its epilogue on the tensor cores), or, with ``DLGO_FUSED_BIAS_ACT=0``,
+    in a launch of their own on its fp32 result."""
 
     can_defer_bias = True
 
@@ -98,7 +103,10 @@ class ReluSquaredMLP(FeedForward):
 
     def forward(self, x: Any, residual: torch.Tensor, ctx: Any, defer_bias: bool = False) -> None:
         """``defer_bias``: the caller adds :attr:`output_bias` itself (fused into its next pass over the result)."""
-        h = K.bias_act(self.w_up(x, STORE_F32), self.b_up, K.ACT_RELU2, self.w_down.weight.dtype)
+        if _FUSED_BIAS_ACT:
+            h = self.w_up.bias_act(x, self.b_up, K.ACT_RELU2)      # bias and relu squared in the contraction's epilogue
+        else:
+            h = K.bias_act(self.w_up(x, STORE_F32), self.b_up, K.ACT_RELU2, self.w_down.weight.dtype)
         if self.output_bias is not None and not defer_bias:
             K.bias_act(residual, self.output_bias, K.ACT_NONE, torch.float32, in_place=True)
         self.w_down(h, ADD_F32, residual)

@@ -39,6 +39,13 @@ class Linear:
             return self._tc(x, epilogue, out)
         return K.gemm_simt(x, self.weight, epilogue, out)
 
+    def bias_act(self, x: torch.Tensor, bias: Optional[torch.Tensor], act: int) -> torch.Tensor:
+        """``act(x . W^T + bias)`` in the activation type; bias and activation run in fp32: in the tensor-core
+        contraction's epilogue where that kernel has the weight, else on the fp32 result of the fp32-pipe kernel."""
+        if self._tc is not None and not self.fuses_swiglu:
+            return self._tc.bias_act(x, bias, act)
+        return K.bias_act(K.gemm_simt(x, self.weight, STORE_F32), bias, act, self.weight.dtype)
+
     def rope_qkv_takes(self, tokens: int, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int) -> bool:
         """Whether, for this many tokens, this weight can run as the q|k|v projection whose epilogue rotates q and
         k (whole head, split-half pairs) and appends k and v to the cache (tensor-core kernel, many tokens)."""

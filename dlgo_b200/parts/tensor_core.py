@@ -130,6 +130,23 @@ class TensorCorePlan:
         bn, pair = self.many_token_shape(t)
         return K.gemm_tc(x, self.weight, out, False, epi, bn, static_operand=2, pair_tile=pair)
 
+    def bias_act(self, x, bias: Optional[torch.Tensor], act: int) -> torch.Tensor:
+        """``act(x . W^T + bias)`` as bfloat16 [tokens, out], bias and activation in the contraction's epilogue
+        (fp32, on the accumulator)."""
+        t = x.shape[0]
+        out = torch.empty((t, self.n), dtype=torch.bfloat16, device=x.device)
+        if t <= SKINNY_MAX:
+            # (K-slices meet in the workspace and the last CTA of a tile applies the epilogue: as many CTAs as
+            # for a plain store)
+            bn, splits = skinny_shape(t, self.n, self.k, self.weight.device, False)
+            ws = cnt = None
+            if splits > 1:
+                ws = _workspace(x.device, K.gemm_tc_workspace_floats(self.n, t, bn, splits))
+                cnt = _counter_buffer(x.device)
+            return K.gemm_tc_bias_act(self.weight, x, out, True, bn, bias, act, splits, ws, cnt, static_operand=1)
+        bn, pair = self.many_token_shape(t)
+        return K.gemm_tc_bias_act(x, self.weight, out, False, bn, bias, act, static_operand=2, pair_tile=pair)
+
     def many_token_shape(self, tokens: int) -> tuple[int, int]:
         """(tile width, CTA-pair tile or 0) for more than SKINNY_MAX tokens: the activations are the M operand."""
         bn = 256 if self.n > 128 else 128

@@ -513,3 +513,27 @@ def test_trace_replay_command(dirs, tmp_path):
     for i, ref in want.items():
         got = torch.from_numpy(np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, V))
         assert_rows(got, ref, "float32", f"step {i}")
+
+
+@pytest.mark.parametrize("tokens", [1, 8, 17, 64, 65, 300])
+@pytest.mark.parametrize("n, k", [(384, 320), (200, 96), (1024, 512)])
+def test_contraction_with_bias_and_activation(tokens, n, k):
+    """The tensor-core contraction's bias + activation epilogue (few tokens: weight rows as the tile's rows, with
+    and without K-slices; many tokens: weight rows as its columns) against fp32 arithmetic."""
+    from dlgo_b200.csrc import kernels as K
+    from dlgo_b200.engine.runtime import Runtime
+    from dlgo_b200.parts.linear import Linear
+    g = torch.Generator().manual_seed(tokens + n)
+    dev = _dev()
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).to(torch.bfloat16)
+    x = torch.randn(tokens, k, generator=g).to(torch.bfloat16)
+    b = torch.randn(n, generator=g)
+    lin = Linear(w.to(dev), Runtime("cuda:0", "bfloat16"))
+    z = x.double() @ w.double().T + b.double()
+    for act, want in ((K.ACT_RELU2, torch.relu(z) ** 2), (K.ACT_NONE, z), (K.ACT_SILU, P.silu(z)), (K.ACT_GELU_TANH, P.gelu_tanh(z))):
+        got = lin.bias_act(x.to(dev), b.to(dev), act)
+        assert got.dtype == torch.bfloat16 and tuple(got.shape) == (tokens, n)
+        assert float((got.float().cpu().double() - want).abs().max()) <= 1e-2 * float(want.abs().max())
+    got = lin.bias_act(x.to(dev), None, K.ACT_RELU2)
+    want = torch.relu(x.double() @ w.double().T) ** 2
+    assert float((got.float().cpu().double() - want).abs().max()) <= 1e-2 * float(want.abs().max())
