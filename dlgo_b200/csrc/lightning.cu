@@ -6,8 +6,8 @@
 // The state of a sequence lives in its slot of the state area between steps, so a prompt may arrive in any
 // number of portions and decoding continues where the prompt stopped.
 //
-// lightning_scan: one block per (sequence, head); the state sits in shared memory while the block walks the
-// sequence's tokens of this step in order.  The projections arrive as fp32 rows [q | k | v | ...]; silu,
+// lightning_scan: one block per (sequence, head, run of value columns); its part of the state sits in shared
+// memory while the block walks the sequence's tokens of this step in order.  The projections arrive as fp32 rows [q | k | v | ...]; silu,
 // decay, state and output are fp32.
 #include "common.cuh"
 
@@ -18,48 +18,50 @@ __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z));
 __global__ void lightning_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off,
                                       const int* __restrict__ tiles, const int* __restrict__ seq_slot,
                                       const float* __restrict__ decay, float* __restrict__ state,
-                                      float* __restrict__ out, int ldo, int H, int dk, int dv) {
+                                      float* __restrict__ out, int ldo, int H, int dk, int dv, int dvc) {
   pdl_launch_dependents();
   extern __shared__ float smem[];
-  float* S = smem;                       // [dk][dv]
-  float* qk = S + (size_t)dk * dv;       // two buffers of [q (dk) | k (dk) | v (dv)]
-  const int per = 2 * dk + dv;
+  // the block's columns [e0, e0 + n) of the state (columns are independent of one another)
+  const int e0 = blockIdx.z * dvc, n = min(dvc, dv - e0);
+  float* S = smem;                       // [dk][n]
+  float* qk = S + (size_t)dk * dvc;      // two buffers of [q (dk) | k (dk) | v (n)]
+  const int per = 2 * dk + dvc;
   const int h = blockIdx.y;
   const int seq = tiles[blockIdx.x * 3 + 0], first = tiles[blockIdx.x * 3 + 1], count = tiles[blockIdx.x * 3 + 2];
   const int slot = seq_slot[seq];
   const float lam = decay[h];
   float* st = state + ((size_t)slot * H + h) * dk * dv;
   pdl_wait();
-  for (int i = threadIdx.x; i < dk * dv; i += blockDim.x) S[i] = st[i];
+  for (int i = threadIdx.x; i < dk * n; i += blockDim.x) S[i] = st[(size_t)(i / n) * dv + e0 + i % n];
   auto fetch = [&](int tok, float* buf) {
     const float* row = proj + (size_t)tok * ld;
-    for (int i = threadIdx.x; i < per; i += blockDim.x) {
-      const int col = i < dk ? q_off + h * dk + i : (i < 2 * dk ? k_off + h * dk + (i - dk) : v_off + h * dv + (i - 2 * dk));
+    for (int i = threadIdx.x; i < 2 * dk + n; i += blockDim.x) {
+      const int col = i < dk ? q_off + h * dk + i : (i < 2 * dk ? k_off + h * dk + (i - dk) : v_off + h * dv + e0 + (i - 2 * dk));
       buf[i] = silu_f(row[col]);
     }
   };
   fetch(first, qk);
   __syncthreads();
-  for (int n = 0; n < count; ++n) {
-    float* cur = qk + (n & 1) * per;
-    if (n + 1 < count) fetch(first + n + 1, qk + ((n + 1) & 1) * per);
+  for (int t = 0; t < count; ++t) {
+    float* cur = qk + (t & 1) * per;
+    if (t + 1 < count) fetch(first + t + 1, qk + ((t + 1) & 1) * per);
     const float* sq = cur;
     const float* sk = cur + dk;
     const float* sv = cur + 2 * dk;
     // a thread owns columns e of the state: no two threads touch the same element
-    for (int e = threadIdx.x; e < dv; e += blockDim.x) {
+    for (int e = threadIdx.x; e < n; e += blockDim.x) {
       const float v = sv[e];
       float o = 0.f;
       for (int i = 0; i < dk; ++i) {
-        const float s = fmaf(lam, S[i * dv + e], sk[i] * v);
-        S[i * dv + e] = s;
+        const float s = fmaf(lam, S[i * n + e], sk[i] * v);
+        S[i * n + e] = s;
         o = fmaf(s, sq[i], o);
       }
-      out[(size_t)(first + n) * ldo + h * dv + e] = o;
+      out[(size_t)(first + t) * ldo + h * dv + e0 + e] = o;
     }
     __syncthreads();
   }
-  for (int i = threadIdx.x; i < dk * dv; i += blockDim.x) st[i] = S[i];
+  for (int i = threadIdx.x; i < dk * n; i += blockDim.x) st[(size_t)(i / n) * dv + e0 + i % n] = S[i];
 }
 
 // Common qk sizes: a thread keeps its column of the state in registers, and a sequence's tokens of one step
@@ -231,14 +233,17 @@ DLGO_EXPORT int dlgo_lightning_scan(const float* proj, int ld, int q_off, int k_
                                     int ldo, int H, int dk, int dv, cudaStream_t stream) {
   if (n_seqs <= 0) return DLGO_OK;
   if (H <= 0 || dk <= 0 || dv <= 0) return DLGO_ERR_SIZE;
-  const size_t smem = ((size_t)dk * dv + 2 * (2 * dk + dv)) * sizeof(float);
+  // as many of a head's value columns per block as keep the block's part of the state within 96 KB
+  int dvc = dv;
+  while (dvc > 1 && ((size_t)dk * dvc + 2 * (2 * (size_t)dk + dvc)) * sizeof(float) > 96 * 1024) dvc = (dvc + 1) / 2;
+  const size_t smem = ((size_t)dk * dvc + 2 * (2 * (size_t)dk + dvc)) * sizeof(float);
   if (smem > 200 * 1024) return DLGO_ERR_SIZE;
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(lightning_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  int threads = ((dv + 31) / 32) * 32;
+  int threads = ((dvc + 31) / 32) * 32;
   if (threads > 256) threads = 256;
   if (threads < 64) threads = 64;
-  launch_kernel(lightning_scan_kernel, dim3(n_seqs, H), dim3(threads), smem, stream, proj, ld, q_off, k_off, v_off,
-                tiles, seq_slot, decay, state, out, ldo, H, dk, dv);
+  launch_kernel(lightning_scan_kernel, dim3(n_seqs, H, (dv + dvc - 1) / dvc), dim3(threads), smem, stream, proj, ld,
+                q_off, k_off, v_off, tiles, seq_slot, decay, state, out, ldo, H, dk, dv, dvc);
   return launch_status();
 }

@@ -329,10 +329,10 @@ def test_sink_counts_once_and_unscaled(dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("decay", [[1.0, 0.0, 0.5], [0.999, 0.9, 0.99]])
-@pytest.mark.parametrize("dim, vdim", [(16, 24), (32, 40), (64, 160), (128, 16)])
+@pytest.mark.parametrize("dim, vdim", [(16, 24), (32, 40), (64, 160), (128, 16), (200, 160)])
 def test_lightning_state_is_carried(dim, vdim, decay, dtype):
     """qk sizes of both kernels (the state in shared memory; in registers with a prompt cut into segments that
-    run side by side), value sizes below, at and above a block's columns."""
+    run side by side), value sizes below, at and above a block's columns, and a state too large for one block."""
     layer = {"type": "lightning", "mixer": {"heads": 3, "dim": dim, "vdim": vdim, "decay": decay}}
     cfg = one_layer(layer, streams=2)
     w = make_weights(cfg, 8)
