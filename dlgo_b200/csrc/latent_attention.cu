@@ -273,6 +273,10 @@ constexpr int LP_UNROLL = 4;
 template <typename T> struct Vec16;
 template <> struct Vec16<float> {
   static constexpr int V = 4;
+  __device__ static __forceinline__ uint4 raw(const float* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+  __device__ static __forceinline__ void unpack(const uint4& u, float* o) {
+    o[0] = __uint_as_float(u.x); o[1] = __uint_as_float(u.y); o[2] = __uint_as_float(u.z); o[3] = __uint_as_float(u.w);
+  }
   __device__ static __forceinline__ void load(const float* p, float* o) {
     const float4 v = *reinterpret_cast<const float4*>(p);
     o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
@@ -280,6 +284,15 @@ template <> struct Vec16<float> {
 };
 template <> struct Vec16<__nv_bfloat16> {
   static constexpr int V = 8;
+  __device__ static __forceinline__ uint4 raw(const __nv_bfloat16* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+  __device__ static __forceinline__ void unpack(const uint4& u, float* o) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __bfloat1622float2(h[k]);
+      o[2 * k] = f.x; o[2 * k + 1] = f.y;
+    }
+  }
   __device__ static __forceinline__ void load(const __nv_bfloat16* p, float* o) {
     const uint4 u = *reinterpret_cast<const uint4*>(p);
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
@@ -324,27 +337,42 @@ latent_partial_kernel(const float* __restrict__ q_lat, const T* __restrict__ pag
     }
   }
   float m = -INFINITY, l = 0.f;
+  // page numbers run one group ahead of the rows: a group costs one round trip to memory, not two
+  int page_next[LP_UNROLL];
+#pragma unroll
+  for (int u = 0; u < LP_UNROLL; ++u) {
+    const int j = j0 + warp * LP_UNROLL + u;
+    page_next[u] = j < j1 ? table[j / page_size] : 0;
+  }
   for (int jb = j0 + warp * LP_UNROLL; jb < j1; jb += LP_WARPS * LP_UNROLL) {
     int page[LP_UNROLL];
 #pragma unroll
-    for (int u = 0; u < LP_UNROLL; ++u) page[u] = (jb + u < j1) ? table[(jb + u) / page_size] : 0;
-    const T* row[LP_UNROLL];
+    for (int u = 0; u < LP_UNROLL; ++u) {
+      page[u] = page_next[u];
+      const int jn = jb + LP_WARPS * LP_UNROLL + u;
+      page_next[u] = jn < j1 ? table[jn / page_size] : 0;
+    }
+    // Every fetch of the group is issued before any of them is used: no branch stands between them.  A key
+    // beyond the slice's end stands in as the slice's last key (written, finite) and gets weight zero below;
+    // a lane beyond the rank reads the row's start against a zero query.
+    uint4 raw[LP_UNROLL][CH];
 #pragma unroll
-    for (int u = 0; u < LP_UNROLL; ++u)
-      row[u] = pages + ((size_t)page[u] * page_size + ((jb + u < j1) ? (jb + u) % page_size : 0)) * rank;
+    for (int u = 0; u < LP_UNROLL; ++u) {
+      const bool in = jb + u < j1;
+      const int j = in ? jb + u : j1 - 1;
+      const int pg = in ? page[u] : table[j / page_size];
+      const T* row = pages + ((size_t)pg * page_size + j % page_size) * rank;
+#pragma unroll
+      for (int i = 0; i < CH; ++i) {
+        const int r = (i * 32 + lane) * V;
+        raw[u][i] = Vec16<T>::raw(row + (r < rank ? r : 0));
+      }
+    }
     float cv[LP_UNROLL][CH][V];
 #pragma unroll
     for (int u = 0; u < LP_UNROLL; ++u)
 #pragma unroll
-      for (int i = 0; i < CH; ++i) {
-        const int r = (i * 32 + lane) * V;
-        if (jb + u < j1 && r < rank) {
-          Vec16<T>::load(row[u] + r, cv[u][i]);
-        } else {
-#pragma unroll
-          for (int k = 0; k < V; ++k) cv[u][i][k] = 0.f;
-        }
-      }
+      for (int i = 0; i < CH; ++i) Vec16<T>::unpack(raw[u][i], cv[u][i]);
     float sc[LP_UNROLL];
 #pragma unroll
     for (int u = 0; u < LP_UNROLL; ++u) {
@@ -435,20 +463,24 @@ latent_out_kernel(const float* __restrict__ parts, const T* __restrict__ w_v, co
     __syncthreads();
     for (int tt = warp; tt < nt; tt += LO_COLS) {               // a warp brings a token's slices together
       const float* p = parts + ((size_t)(t0 + tt) * H + h) * n_slices * (rank + 2);
-      float M = sk;
-      for (int s = 0; s < n_slices; ++s) M = fmaxf(M, p[(size_t)s * (rank + 2)]);
+      // lane s holds slice s (at most 32 slices): its maximum and sum, then its factor
+      const float ms = lane < n_slices ? p[(size_t)lane * (rank + 2)] : -INFINITY;
+      const float ls = lane < n_slices ? p[(size_t)lane * (rank + 2) + 1] : 0.f;
+      const float M = fmaxf(warp_max(ms), sk);
+      const float es = ms == -INFINITY ? 0.f : expf(ms - M);
+      // slices in slice order: lane 0 adds them up one after another
       float L = sink ? expf(sk - M) : 0.f;
-      for (int s = 0; s < n_slices; ++s) {
-        const float ms = p[(size_t)s * (rank + 2)];
-        L = fmaf(p[(size_t)s * (rank + 2) + 1], ms == -INFINITY ? 0.f : expf(ms - M), L);
-      }
-      const float inv = 1.0f / L;
-      for (int r = lane; r < rank; r += 32) s_lat[tt * rank + r] = 0.f;
-      for (int s = 0; s < n_slices; ++s) {                      // slices in slice order
-        const float ms = p[(size_t)s * (rank + 2)];
-        const float fs = ms == -INFINITY ? 0.f : expf(ms - M) * inv;
-        const float* ps = p + (size_t)s * (rank + 2) + 2;
-        for (int r = lane; r < rank; r += 32) s_lat[tt * rank + r] = fmaf(ps[r], fs, s_lat[tt * rank + r]);
+      for (int q = 0; q < n_slices; ++q) L = fmaf(__shfl_sync(0xffffffffu, ls, q), __shfl_sync(0xffffffffu, es, q), L);
+      const float f = es / L;
+      for (int r0 = 0; r0 < rank; r0 += 32) {                  // (the whole warp stays in the loop: it shuffles)
+        const int r = r0 + lane;
+        float a = 0.f;
+#pragma unroll 4
+        for (int q = 0; q < n_slices; ++q) {
+          const float fq = __shfl_sync(0xffffffffu, f, q);
+          if (r < rank) a = fmaf(p[(size_t)q * (rank + 2) + 2 + r], fq, a);
+        }
+        if (r < rank) s_lat[tt * rank + r] = a;
       }
     }
     __syncthreads();
@@ -603,7 +635,7 @@ DLGO_EXPORT int dlgo_latent_attention_few(const void* q, int q_is_f32, int ldq, 
                                           float* parts, cudaStream_t stream) {
   if (T_tokens <= 0) return DLGO_OK;
   if (H <= 0 || dk <= 0 || dv <= 0 || rank <= 0 || page_size <= 0 || window < 0 || n_slices < 1 ||
-      n_slices > 65535 || H > 65535)
+      n_slices > 32 || H > 65535)      // (a lane per slice where the slices meet)
     return DLGO_ERR_SIZE;
   if (((uintptr_t)pages & 15) || ((uintptr_t)w_v & 15)) return DLGO_ERR_ALIGN;
   if (dtype == DLGO_F32) return latent_few_by_rank<float>(FEW_ARGS);
