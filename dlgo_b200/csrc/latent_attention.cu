@@ -474,12 +474,11 @@ latent_out_kernel(const float* __restrict__ parts, const T* __restrict__ w_v, co
       const float f = es / L;
       for (int r0 = 0; r0 < rank; r0 += 32) {                  // (the whole warp stays in the loop: it shuffles)
         const int r = r0 + lane;
+        const float* col = p + 2 + (r < rank ? r : 0);          // (no branch between the fetches)
         float a = 0.f;
 #pragma unroll 4
-        for (int q = 0; q < n_slices; ++q) {
-          const float fq = __shfl_sync(0xffffffffu, f, q);
-          if (r < rank) a = fmaf(p[(size_t)q * (rank + 2) + 2 + r], fq, a);
-        }
+        for (int q = 0; q < n_slices; ++q)
+          a = fmaf(col[(size_t)q * (rank + 2)], __shfl_sync(0xffffffffu, f, q), a);
         if (r < rank) s_lat[tt * rank + r] = a;
       }
     }
