@@ -4,8 +4,9 @@ from .registry import (ConfigError, config_class_for, config_from_dict, load_con
 from .spec import ArchitectureSpec, LayerSpec, PartSpec, RunEntry
 from .llama import LlamaConfig, RopeScaling
 from .dedutar import DedutarConfig
+from .monolix import MonolixConfig
 
 __all__ = [
-    "ArchitectureSpec", "ConfigError", "DedutarConfig", "LayerSpec", "LlamaConfig", "PartSpec", "RopeScaling", "RunEntry",
+    "ArchitectureSpec", "ConfigError", "DedutarConfig", "LayerSpec", "LlamaConfig", "MonolixConfig", "PartSpec", "RopeScaling", "RunEntry",
     "config_class_for", "config_from_dict", "load_config", "register_architecture", "registered_architectures",
 ]

@@ -42,6 +42,9 @@ LIBRARIES: Dict[str, List[str]] = {
     "streams": ["streams.cu"],
     "latent_attention": ["latent_attention.cu"],
     "lightning": ["lightning.cu"],
+    "headnorm_rope": ["headnorm_rope.cu"],
+    "postnorm": ["postnorm.cu"],
+    "moe": ["moe.cu"],
 }
 _HEADERS = ["common.cuh", "attention_noalloc.h", "attention_combine.cuh", "attention_decode_tiles.cuh", "tcgen05.cuh"]
 

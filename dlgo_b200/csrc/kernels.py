@@ -526,6 +526,185 @@ def rope_append(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, token_p
     _check(st, "rope_append")
 
 
+# ------------------------------------------- head norm + rotation from frequencies + append
+def headnorm_rope_append(proj: torch.Tensor, bias: Optional[torch.Tensor], w_q: Optional[torch.Tensor],
+                         w_k: Optional[torch.Tensor], eps: float, freq: Optional[torch.Tensor], rotary_dim: int,
+                         token_pos: torch.Tensor, token_seq: torch.Tensor, seq_slot: torch.Tensor,
+                         page_table: torch.Tensor, kpages: torch.Tensor, vpages: torch.Tensor, num_heads: int,
+                         num_kv_heads: int, head_dim: int, values_from_keys: bool, write_cache: bool = True,
+                         clear: bool = False) -> torch.Tensor:
+    """From the fp32 projection ``proj`` [T, ld] (query heads, key heads and, unless ``values_from_keys``, value
+    heads; ``bias`` fp32 per column added first): per-head RMS norm of queries and keys with the weights ``w_q`` /
+    ``w_k`` (None: no norm), rotation of the first ``rotary_dim`` numbers of each head (pairs (i, i + rotary_dim/2))
+    by the fp32 angle ``float(position) * freq[i]``, keys and values stored at their positions' pages (with
+    ``values_from_keys`` a value is its key as projected, before norm and rotation).  Returns the queries
+    [T, heads * head_dim] in the cache's type.  ``clear`` leaves zeros in ``proj``."""
+    if proj.dtype != torch.float32 or proj.dim() != 2 or proj.stride(1) != 1:
+        raise KernelError("headnorm_rope_append: proj must be 2-D float32 with unit inner stride")
+    for n, t in (("bias", bias), ("w_q", w_q), ("w_k", w_k), ("freq", freq)):
+        if t is not None:
+            _need(t, torch.float32, n)
+    for n, t in (("token_pos", token_pos), ("token_seq", token_seq), ("seq_slot", seq_slot), ("page_table", page_table)):
+        _need(t, torch.int32, n)
+    _need(kpages, None, "kpages")
+    _need(vpages, kpages.dtype, "vpages")
+    T = proj.shape[0]
+    cols = (num_heads + (1 if values_from_keys else 2) * num_kv_heads) * head_dim
+    if proj.shape[1] < cols or (bias is not None and bias.numel() != cols):
+        raise KernelError(f"headnorm_rope_append: the projection (and its bias) must have {cols} columns")
+    for n, t in (("w_q", w_q), ("w_k", w_k)):
+        if t is not None and t.numel() != head_dim:
+            raise KernelError(f"headnorm_rope_append: {n} must have head_dim elements")
+    if rotary_dim and (freq is None or freq.numel() != rotary_dim // 2):
+        raise KernelError("headnorm_rope_append: one frequency per rotated pair")
+    if kpages.shape[-1] != head_dim or kpages.shape[-3] != num_kv_heads:
+        raise KernelError("headnorm_rope_append: the cache's pages do not fit the heads")
+    q = torch.empty((T, num_heads * head_dim), dtype=kpages.dtype, device=proj.device)
+    st = _lib("headnorm_rope").dlgo_headnorm_rope_append(
+        _ptr(proj), _i(proj.stride(0)), _ptr(bias), _ptr(w_q), _ptr(w_k), _f(eps), _ptr(freq), _i(rotary_dim),
+        _ptr(token_pos), _ptr(token_seq), _ptr(seq_slot), _ptr(page_table), _i(page_table.shape[1]), _ptr(kpages),
+        _ptr(vpages), _ptr(q), _i(dtype_code(kpages.dtype)), _i(T), _i(num_heads), _i(num_kv_heads), _i(head_dim),
+        _i(kpages.shape[-2]), _i(1 if values_from_keys else 0), _i(1 if write_cache else 0), _i(1 if clear else 0),
+        _stream())
+    _check(st, "headnorm_rope_append")
+    return q
+
+
+# ------------------------------------------------------- norm after the residual sum
+def scaled_add_rmsnorm(x: torch.Tensor, y: Optional[torch.Tensor], layer_scale: Optional[torch.Tensor],
+                       w: Optional[torch.Tensor], skip: float, eps: float, act_dtype: Optional[torch.dtype],
+                       clear_y: bool = True) -> Optional[torch.Tensor]:
+    """``x <- rms(skip * x + layer_scale * y) * w`` on the fp32 residual stream ``x`` [T, d], in place (``y`` fp32
+    [T, d], left zero with ``clear_y``); returns the new rows in ``act_dtype`` (None: no copy).  With ``y`` and ``w``
+    None only the copy is made."""
+    _need(x, torch.float32, "x")
+    T, d = x.shape
+    for n, t in (("y", y), ("layer_scale", layer_scale), ("w", w)):
+        if t is not None:
+            _need(t, torch.float32, n)
+    if y is not None and tuple(y.shape) != (T, d):
+        raise KernelError("scaled_add_rmsnorm: y must have x's shape")
+    for n, t in (("layer_scale", layer_scale), ("w", w)):
+        if t is not None and t.numel() != d:
+            raise KernelError(f"scaled_add_rmsnorm: {n} must have one element per channel")
+    act = None if act_dtype is None else torch.empty((T, d), dtype=act_dtype, device=x.device)
+    st = _lib("postnorm").dlgo_scaled_add_rmsnorm(
+        _ptr(x), _ptr(y), _ptr(layer_scale), _ptr(w), _ptr(act), _i(dtype_code(act_dtype or torch.float32)), _i(T),
+        _i(d), _f(skip), _f(eps), _i(1 if clear_y else 0), _stream())
+    _check(st, "scaled_add_rmsnorm")
+    return act
+
+
+# ------------------------------------------------------------------ routed experts
+MOE_FEW_ROWS, MOE_TILE_ROWS = 8, 64          # rows per tile of the two grouped contractions
+
+
+def moe_router(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], n_outputs: int,
+               has_gate: bool, top: int, groups: int, keep: int, sigmoid_scores: bool = False,
+               renormalize: bool = False):
+    """Router of a mixture of experts for ``h`` [T, d]: returns (chosen outputs [T, top] int32, their weights
+    [T, top] fp32, gate [T] fp32 or None).  ``w_router`` is fp32 [n_outputs (+ 1 gate row), d]."""
+    _need(w_router, torch.float32, "w_router")
+    if h.dim() != 2 or h.stride(1) != 1:
+        raise KernelError("moe_router: h must be 2-D with unit inner stride")
+    T, d = h.shape
+    rows = n_outputs + (1 if has_gate else 0)
+    if tuple(w_router.shape) != (rows, d):
+        raise KernelError(f"moe_router: the router's weight must be [{rows}, {d}]")
+    if correction is not None:
+        _need(correction, torch.float32, "correction")
+        if correction.numel() != n_outputs:
+            raise KernelError("moe_router: one correction per router output")
+    idx = torch.empty((T, top), dtype=torch.int32, device=h.device)
+    wt = torch.empty((T, top), dtype=torch.float32, device=h.device)
+    gate = torch.empty((T,), dtype=torch.float32, device=h.device) if has_gate else None
+    st = _lib("moe").dlgo_moe_router(
+        _ptr(h), _i(dtype_code(h.dtype)), _i(h.stride(0)), _ptr(w_router), _ptr(correction), _ptr(idx), _ptr(wt),
+        _ptr(gate), _i(T), _i(d), _i(n_outputs), _i(1 if has_gate else 0), _i(top), _i(groups), _i(keep),
+        _i(1 if sigmoid_scores else 0), _i(1 if renormalize else 0), _stream())
+    _check(st, "moe_router")
+    return idx, wt, gate
+
+
+class MoEPlan:
+    """Device-side lists of a step's (token, choice) pairs sorted by expert (see :func:`moe_plan`)."""
+
+    __slots__ = ("offsets", "sorted_pair", "tile_expert", "tile_row0", "n_tiles", "max_tiles", "tile_rows", "pairs")
+
+
+def moe_plan(idx: torch.Tensor, n_experts: int, tile_rows: int) -> MoEPlan:
+    """Sort the pairs of ``idx`` [T, top] by expert, on the device: offsets per expert, the sorted list of pair
+    numbers (token * top + choice), and row tiles of ``tile_rows`` rows.  Outputs >= ``n_experts`` enter no list."""
+    _need(idx, torch.int32, "idx")
+    pairs = idx.numel()
+    p = MoEPlan()
+    p.pairs, p.tile_rows = pairs, tile_rows
+    p.max_tiles = (pairs + tile_rows - 1) // tile_rows + n_experts
+    buf = torch.empty((n_experts + 1 + pairs + 2 * p.max_tiles + 1,), dtype=torch.int32, device=idx.device)
+    o = 0
+    p.offsets = buf[o:o + n_experts + 1]; o += n_experts + 1
+    p.sorted_pair = buf[o:o + pairs]; o += pairs
+    p.tile_expert = buf[o:o + p.max_tiles]; o += p.max_tiles
+    p.tile_row0 = buf[o:o + p.max_tiles]; o += p.max_tiles
+    p.n_tiles = buf[o:o + 1]
+    st = _lib("moe").dlgo_moe_plan(_ptr(idx), _i(pairs), _i(n_experts), _i(tile_rows), _ptr(p.offsets),
+                                   _ptr(p.sorted_pair), _ptr(p.tile_expert), _ptr(p.tile_row0), _ptr(p.n_tiles),
+                                   _i(p.max_tiles), _stream())
+    _check(st, "moe_plan")
+    return p
+
+
+def moe_gemm(plan: MoEPlan, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gather_div: Optional[int],
+             scatter: bool, act: int) -> torch.Tensor:
+    """Grouped contraction over the plan's sorted rows: ``out[o(r)] = act(a[s(r)] . w[expert(r)]^T)`` with ``w``
+    [experts, N, K].  ``gather_div`` d: ``s(r) = pair(r) // d`` (rows of ``a`` are tokens), None: ``s(r) = r``;
+    ``scatter``: ``o(r) = pair(r)``, else ``o(r) = r``.  ``out`` is fp32 or ``a``'s type."""
+    _need(w, a.dtype, "w")
+    if a.dim() != 2 or a.stride(1) != 1 or out.dim() != 2 or out.stride(1) != 1 or w.dim() != 3:
+        raise KernelError("moe_gemm: a and out must be 2-D with unit inner stride, w [experts, N, K]")
+    _need(w, None, "w")
+    E, N, Kd = w.shape
+    if a.shape[1] != Kd or out.shape[1] != N or out.dtype not in (torch.float32, a.dtype):
+        raise KernelError("moe_gemm: shapes or types do not fit")
+    kind = 0 if plan.tile_rows == MOE_FEW_ROWS else 1
+    if kind == 1 and plan.tile_rows != MOE_TILE_ROWS:
+        raise KernelError(f"moe_gemm: the plan's tiles must have {MOE_FEW_ROWS} or {MOE_TILE_ROWS} rows")
+    st = _lib("moe").dlgo_moe_gemm(
+        _i(kind), _i(dtype_code(a.dtype)), _ptr(a), _ll(a.stride(0)), _ptr(plan.sorted_pair if gather_div else None),
+        _i(gather_div or 1), _ptr(w), _ptr(out), _ll(out.stride(0)), _ptr(plan.sorted_pair if scatter else None),
+        _ptr(plan.offsets), _ptr(plan.tile_expert), _ptr(plan.tile_row0), _ptr(plan.n_tiles), _i(plan.max_tiles),
+        _i(N), _i(Kd), _i(act), _i(1 if out.dtype == torch.float32 else 0), _stream())
+    _check(st, "moe_gemm")
+    return out
+
+
+def moe_combine(y: torch.Tensor, pair_out: Optional[torch.Tensor], h: torch.Tensor, idx: torch.Tensor,
+                wt: torch.Tensor, n_experts: int, shared: Optional[torch.Tensor] = None,
+                gate: Optional[torch.Tensor] = None) -> None:
+    """``y[t] += sum_k wt[t, k] * (pair_out[t * top + k] if idx[t, k] < n_experts else h[t]) + gate[t] * shared[t]``
+    (fp32; ``gate`` None: 1)."""
+    _need(y, torch.float32, "y")
+    _need(idx, torch.int32, "idx")
+    _need(wt, torch.float32, "wt")
+    T, d = y.shape
+    top = idx.shape[1]
+    if h.dim() != 2 or h.stride(1) != 1 or tuple(h.shape) != (T, d):
+        raise KernelError("moe_combine: h must be [T, d] with unit inner stride")
+    if pair_out is not None:
+        _need(pair_out, torch.float32, "pair_out")
+        if tuple(pair_out.shape) != (T * top, d):
+            raise KernelError("moe_combine: pair_out must be [T * top, d]")
+    elif n_experts > 0:
+        raise KernelError("moe_combine: experts without their outputs")
+    for n, t in (("shared", shared), ("gate", gate)):
+        if t is not None:
+            _need(t, torch.float32, n)
+    st = _lib("moe").dlgo_moe_combine(_ptr(y), _ptr(pair_out), _ptr(h), _i(dtype_code(h.dtype)), _i(h.stride(0)),
+                                      _ptr(idx), _ptr(wt), _ptr(shared), _ptr(gate), _i(T), _i(d), _i(top),
+                                      _i(n_experts), _stream())
+    _check(st, "moe_combine")
+
+
 # ------------------------------------------------------------------- attention
 ATT_ROW_ELEMS = 128 * 32  # rows of a block times head_dim may not exceed this
 
@@ -859,9 +1038,10 @@ def check_device_errors() -> None:
                               "invalid and its counters must be zeroed again (build a new engine)")
         if v != 0:
             raise KernelError("a token's position had no page in the cache's table (persistent decode kernel)")
-    if "rope_append" in build._loaded and build._loaded["rope_append"].dlgo_rope_append_error() != 0:
-        raise KernelError("a token's position had no page in the cache's table: its keys and values were not "
-                          "stored and the step's results are invalid")
+    for lib, fn in (("rope_append", "dlgo_rope_append_error"), ("headnorm_rope", "dlgo_headnorm_rope_error")):
+        if lib in build._loaded and getattr(build._loaded[lib], fn)() != 0:
+            raise KernelError("a token's position had no page in the cache's table: its keys and values were not "
+                              "stored and the step's results are invalid")
 
 
 # ------------------------------------------------------------ decode attention

@@ -21,7 +21,7 @@ import torch
 
 from ..csrc import kernels as K
 from .base import CacheNeed, Mixer, ParamSpec, PositionEncoding
-from .linear import ADD_F32, STORE, Linear
+from .linear import ADD_F32, STORE, STORE_F32, Linear
 from .registry import MIXERS
 
 _CLUSTER_MAX = int(os.environ.get("DLGO_ATTN_CLUSTER_MAX", 8))     # slices up to this many combine in a cluster
@@ -121,6 +121,62 @@ class GQAAttention(Mixer):
                 self.wqkv.rope_qkv_takes(ctx.n_tokens, self.num_heads, self.num_kv_heads, self.head_dim,
                                          cache.page_size))
 
+    def _decode_plan(self, ctx: Any, cache: Any, act: torch.dtype):
+        """(decode kernel?, tensor-core decode kernel?, page slices, scratch, counters, pages of the longest
+        sequence) for this step's attention."""
+        T = ctx.n_tokens
+        group = self.num_heads // self.num_kv_heads
+        longest = ctx.capacity if ctx.captured else ctx.max_len
+        pages = max(1, (longest + cache.page_size - 1) // cache.page_size)
+        decode_kernel = ctx.decode and K.attention_decode_takes(act, self.head_dim, cache.page_size)
+        n_splits, scratch, counters = self._decode_slices(ctx, cache, T, group, pages) if decode_kernel else (1, None, None)
+        mma = (decode_kernel and _MMA_KEYS > 0 and
+               K.attention_decode_mma_takes(act, self.head_dim, cache.page_size, n_splits))
+        return decode_kernel, mma, n_splits, scratch, counters, pages
+
+    def _attend(self, qkv: torch.Tensor, ctx: Any, cache: Any, out: torch.Tensor, decode_kernel: bool, mma: bool,
+                n_splits: int, scratch: Any, counters: Any, pages: int) -> None:
+        """Attention of the step's (rotated) queries, the first columns of ``qkv``'s rows, over the cache,
+        into ``out`` [T, heads * head_dim], by whichever kernel takes the step."""
+        T = ctx.n_tokens
+        x = qkv
+        group = self.num_heads // self.num_kv_heads
+        if mma:
+            K.attention_decode_mma(qkv, qkv.stride(0), T, cache.keys, cache.values, cache.page_table, ctx.seq_slot,
+                                   ctx.token_pos, out, self.num_heads, self.num_kv_heads, self.head_dim, self.scale,
+                                   self.window or 0, n_splits, _MMA_KEYS, scratch)
+        elif decode_kernel:
+            K.attention_decode(qkv, qkv.stride(0), T, cache.keys, cache.values, cache.page_table, ctx.seq_slot,
+                               ctx.token_pos, out, self.num_heads, self.num_kv_heads, self.head_dim, self.scale,
+                               self.window or 0, n_splits, scratch, counters)
+        elif not ctx.decode and K.attention_prefill_tc_takes(qkv.dtype, self.head_dim, cache.page_size):
+            # prompts: 128 query rows per CTA on the tensor cores
+            tiles, n_tiles, _ = ctx.tiles(K.PREFILL_TC_TILE, heaviest_first=True)
+            K.attention_prefill_tc(qkv, qkv.stride(0), T, cache.keys, cache.values, cache.page_table, tiles,
+                                   ctx.seq_slot, ctx.token_pos, out, self.num_heads, self.num_kv_heads,
+                                   self.head_dim, self.scale, self.window or 0)
+        else:
+            qt, gchunk = K.attention_tile_shape(self.head_dim, group, ctx.decode)
+            tiles, n_tiles, tile_max = ctx.tiles(qt)
+            n_gchunks = (group + gchunk - 1) // gchunk
+            base_blocks = n_tiles * self.num_kv_heads * n_gchunks
+            target = 2 * _sm_count(x.device)
+            n_splits = max(1, min(pages, -(-target // base_blocks))) if ctx.decode else 1
+            scratch = None
+            if n_splits > 1:
+                scratch = ctx.scratch("attention",
+                                      K.attention_scratch_floats(T, self.num_heads, self.head_dim, n_splits))
+            K.attention(qkv, qkv.stride(0), T, cache.keys, cache.values, cache.page_table, tiles, tile_max,
+                        ctx.seq_slot, ctx.token_pos, out, self.num_heads, self.num_kv_heads, self.head_dim,
+                        self.scale, self.window or 0, n_splits, gchunk, scratch)
+
+    def _project_out(self, out: torch.Tensor, residual: torch.Tensor, ctx: Any) -> None:
+        parts = self.wo.partials(out, for_residual=True) if hasattr(ctx, "defer") else None
+        if parts is not None:
+            ctx.defer(residual, parts)      # the next norm adds the slices to the residual
+        else:
+            self.wo(out, ADD_F32, residual)
+
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: Any, cache: Any,
                 state: Optional[torch.Tensor], positions: Mapping[str, PositionEncoding]) -> None:
         T = ctx.n_tokens
@@ -133,13 +189,8 @@ class GQAAttention(Mixer):
             rot, inter = 0, False
         act = self.wqkv.weight.dtype
         n_cols = self.q_dim + 2 * self.kv_dim
-        longest = ctx.capacity if ctx.captured else ctx.max_len
-        pages = max(1, (longest + cache.page_size - 1) // cache.page_size)
-        decode_kernel = ctx.decode and K.attention_decode_takes(act, self.head_dim, cache.page_size)
-        n_splits, scratch, counters = self._decode_slices(ctx, cache, T, group, pages) if decode_kernel else (1, None, None)
         # bfloat16, common head sizes, one token per sequence: scores and weighted sum on the tensor cores
-        mma = (decode_kernel and _MMA_KEYS > 0 and
-               K.attention_decode_mma_takes(act, self.head_dim, cache.page_size, n_splits))
+        decode_kernel, mma, n_splits, scratch, counters, pages = self._decode_plan(ctx, cache, act)
         out = torch.empty((T, self.q_dim), dtype=act, device=x.device)
         qkv = None
         rotated = False
@@ -178,41 +229,91 @@ class GQAAttention(Mixer):
             K.rope_append(qkv, cos, sin, ctx.token_pos, ctx.token_seq, ctx.seq_slot, cache.page_table, cache.keys,
                           cache.values, self.num_heads, self.num_kv_heads, self.head_dim, rot, inter, cache.writes,
                           qkv_parts, False)
-        if rotated:
-            pass
-        elif mma:
-            K.attention_decode_mma(qkv, qkv.stride(0), T, cache.keys, cache.values, cache.page_table, ctx.seq_slot,
-                                   ctx.token_pos, out, self.num_heads, self.num_kv_heads, self.head_dim, self.scale,
-                                   self.window or 0, n_splits, _MMA_KEYS, scratch)
-        elif decode_kernel:
-            K.attention_decode(qkv, qkv.stride(0), T, cache.keys, cache.values, cache.page_table, ctx.seq_slot,
-                               ctx.token_pos, out, self.num_heads, self.num_kv_heads, self.head_dim, self.scale,
-                               self.window or 0, n_splits, scratch, counters)
-        elif not ctx.decode and K.attention_prefill_tc_takes(qkv.dtype, self.head_dim, cache.page_size):
-            # prompts: 128 query rows per CTA on the tensor cores
-            tiles, n_tiles, _ = ctx.tiles(K.PREFILL_TC_TILE, heaviest_first=True)
-            K.attention_prefill_tc(qkv, qkv.stride(0), T, cache.keys, cache.values, cache.page_table, tiles,
-                                   ctx.seq_slot, ctx.token_pos, out, self.num_heads, self.num_kv_heads,
-                                   self.head_dim, self.scale, self.window or 0)
+        if not rotated:
+            self._attend(qkv, ctx, cache, out, decode_kernel, mma, n_splits, scratch, counters, pages)
+        self._project_out(out, residual, ctx)
+
+
+class KeysAsValuesAttention(GQAAttention):
+    """Grouped-query attention whose values are its keys as projected: there is no value projection, and what a
+    position contributes to the weighted sum is its key BEFORE the head norm and the rotation.
+
+        q = Wq h (+ bq),  k = Wk h (+ bk),  v = k
+        q, k <- head norm (per head: u / sqrt(mean(u^2) + eps) * w, one weight of head_dim numbers shared by all
+                heads; ``head_norm``), then the rotation of the first numbers of each head (the position encoding
+                named by ``position_encoding`` gives how many and at which frequencies)
+        out  = Wo softmax(q . k * scale) v            (causal, over the cache)
+
+    The cache keeps two rows per position and kv head like any grouped-query mixer: the normed and rotated key,
+    and the key as projected (the value).  The projection's result stays fp32 until bias, norm and rotation are
+    done (one kernel, which also appends to the cache); scores, softmax and the weighted sum run in the same
+    attention kernels as :class:`GQAAttention`.  ``names``: tensor names below the part's prefix."""
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+                 bias: bool = False, head_norm: bool = False, eps: float = 1e-6, window: Optional[int] = None,
+                 position_encoding: Optional[str] = None, cache_group: str = "full",
+                 names: Optional[Mapping[str, str]] = None):
+        super().__init__(hidden_size, num_heads, num_kv_heads, head_dim, scale, window, position_encoding, cache_group)
+        self.params.update(bias=bias, head_norm=head_norm, eps=eps, names=names)
+        self.bias = bool(bias)
+        self.head_norm = bool(head_norm)
+        self.eps = float(eps)
+        self.names = {"q": "q_proj.weight", "k": "k_proj.weight", "q_bias": "q_proj.bias", "k_bias": "k_proj.bias",
+                      "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "out": "o_proj.weight"}
+        self.names.update(names or {})
+        self.wqk: Optional[Linear] = None
+        self.b_qk: Optional[torch.Tensor] = None
+        self.w_qnorm: Optional[torch.Tensor] = None
+        self.w_knorm: Optional[torch.Tensor] = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        n = self.names
+        specs = {n["q"]: ParamSpec((self.q_dim, self.hidden_size)), n["k"]: ParamSpec((self.kv_dim, self.hidden_size)),
+                 n["out"]: ParamSpec((self.hidden_size, self.q_dim))}
+        if self.bias:
+            specs[n["q_bias"]] = ParamSpec((self.q_dim,))
+            specs[n["k_bias"]] = ParamSpec((self.kv_dim,))
+        if self.head_norm:
+            specs[n["q_norm"]] = ParamSpec((self.head_dim,), "one_plus_normal")
+            specs[n["k_norm"]] = ParamSpec((self.head_dim,), "one_plus_normal")
+        return specs
+
+    def load(self, get: Callable[[str], torch.Tensor], runtime: Any) -> None:
+        n = self.names
+        self.wqk = Linear(torch.cat([runtime.compute_copy(get(n["q"])), runtime.compute_copy(get(n["k"]))], dim=0), runtime)
+        self.wo = Linear(get(n["out"]), runtime)
+        if self.bias:       # added to the fp32 result of the projection
+            self.b_qk = torch.cat([get(n["q_bias"]).to(torch.float32), get(n["k_bias"]).to(torch.float32)]).contiguous()
+        if self.head_norm:  # norms are 32-bit in every precision
+            self.w_qnorm = get(n["q_norm"]).to(torch.float32).contiguous()
+            self.w_knorm = get(n["k_norm"]).to(torch.float32).contiguous()
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: Any, cache: Any,
+                state: Optional[torch.Tensor], positions: Mapping[str, PositionEncoding]) -> None:
+        T = ctx.n_tokens
+        freq, rot = None, 0
+        if self.position_encoding is not None:
+            pe = positions[self.position_encoding]
+            freq, rot = pe.frequencies, pe.rotary_dim
+        act = self.wqk.weight.dtype
+        n_cols = self.q_dim + self.kv_dim
+        decode_kernel, mma, n_splits, scratch, counters, pages = self._decode_plan(ctx, cache, act)
+        if _QKV_SUM and self.wqk.sums_slices_at_memory(T):
+            # few tokens: the projection's K-slices add themselves into one fp32 sum that is zero between steps;
+            # the norm-and-rotation kernel reads it once and leaves zeros behind
+            proj = ctx.zeros(f"qk_sum{n_cols}", T * n_cols, torch.float32)[:T * n_cols].view(T, n_cols)
+            self.wqk(x, ADD_F32, proj)
+            clear = True
         else:
-            qt, gchunk = K.attention_tile_shape(self.head_dim, group, ctx.decode)
-            tiles, n_tiles, tile_max = ctx.tiles(qt)
-            n_gchunks = (group + gchunk - 1) // gchunk
-            base_blocks = n_tiles * self.num_kv_heads * n_gchunks
-            target = 2 * _sm_count(x.device)
-            n_splits = max(1, min(pages, -(-target // base_blocks))) if ctx.decode else 1
-            scratch = None
-            if n_splits > 1:
-                scratch = ctx.scratch("attention",
-                                      K.attention_scratch_floats(T, self.num_heads, self.head_dim, n_splits))
-            K.attention(qkv, qkv.stride(0), T, cache.keys, cache.values, cache.page_table, tiles, tile_max,
-                        ctx.seq_slot, ctx.token_pos, out, self.num_heads, self.num_kv_heads, self.head_dim,
-                        self.scale, self.window or 0, n_splits, gchunk, scratch)
-        parts = self.wo.partials(out, for_residual=True) if hasattr(ctx, "defer") else None
-        if parts is not None:
-            ctx.defer(residual, parts)      # the next norm adds the slices to the residual
-        else:
-            self.wo(out, ADD_F32, residual)
+            proj = self.wqk(x, STORE_F32)
+            clear = False
+        q = K.headnorm_rope_append(proj, self.b_qk, self.w_qnorm, self.w_knorm, self.eps, freq, rot, ctx.token_pos,
+                                   ctx.token_seq, ctx.seq_slot, cache.page_table, cache.keys, cache.values,
+                                   self.num_heads, self.num_kv_heads, self.head_dim, True, cache.writes, clear)
+        out = torch.empty((T, self.q_dim), dtype=act, device=x.device)
+        self._attend(q, ctx, cache, out, decode_kernel, mma, n_splits, scratch, counters, pages)
+        self._project_out(out, residual, ctx)
 
 
 MIXERS.register("gqa_attention", GQAAttention)
+MIXERS.register("keys_as_values_attention", KeysAsValuesAttention)

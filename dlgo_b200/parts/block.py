@@ -128,6 +128,77 @@ class HyperPreNormBlock(Block):
                 K.streams_step(streams, **write)
 
 
+class LayerScale(Part):
+    """How a sublayer's result y joins the residual stream x in a layer that norms after the sum:
+    ``skip_scale * x + scale * y`` with ``scale`` one learned number per channel and ``skip_scale`` a constant.
+    ``name``: the tensor's name below the part's prefix."""
+
+    def __init__(self, size: int, skip_scale: float = 1.0, name: str = "weight"):
+        super().__init__(size=size, skip_scale=skip_scale, name=name)
+        self.size = int(size)
+        self.skip_scale = float(skip_scale)
+        self.name = name
+        self.scale: Optional[torch.Tensor] = None
+
+    def param_specs(self):
+        return {self.name: ParamSpec((self.size,), "one_plus_normal")}
+
+    def load(self, get: Any, runtime: Any) -> None:
+        self.scale = get(self.name).to(torch.float32).contiguous()      # part of the residual sum: fp32
+
+
+class PostNormBlock(Block):
+    """Norm after the sum: ``x <- norm1(a x + s1 * mixer(x))``, then ``x <- norm2(a x + s2 * ffn(x))``, where the
+    sublayers read x itself and (a, s) come from the sublayer's connection (:class:`LayerScale`).  A layer
+    without a feed-forward ends after the first line.  The residual stream stays fp32; a sublayer adds its result
+    into a zeroed fp32 [tokens, hidden] buffer as it would into a residual stream, and ONE launch forms the sum,
+    norms it, rewrites x, leaves the buffer zero and makes the copy of x in the run's type that the next
+    contractions read."""
+
+    handles_pending = False
+
+    def __init__(self, mixer: Any, ffn: Any, norms: Mapping[str, Any], connections: Any = None):
+        super().__init__(mixer, ffn, norms, connections)
+        if mixer is None:
+            raise ValueError("a block needs a mixer")
+        self.sublayers = []
+        for part, norm, conn in ((mixer, "mixer_norm", "mixer_conn"), (ffn, "ffn_norm", "ffn_conn")):
+            if part is None:
+                continue
+            if norm not in self.norms or conn not in self.connections:
+                raise ValueError(f"a post-norm block needs the norm {norm!r} and the connection {conn!r}")
+            n, c = self.norms[norm], self.connections[conn]
+            if not (hasattr(n, "weight") and hasattr(n, "eps") and hasattr(c, "scale") and hasattr(c, "skip_scale")):
+                raise ValueError(f"a post-norm block needs an RMS norm as {norm!r} and a layer scale as {conn!r}")
+            self.sublayers.append((part, n, c))
+
+    def forward(self, residual: torch.Tensor, ctx: Any, cache: Any, state: Optional[torch.Tensor],
+                positions: Mapping[str, PositionEncoding]) -> None:
+        T, d = residual.shape
+        dtype = ctx.runtime.dtype
+        y = ctx.zeros(f"sublayer_out{d}", T * d, torch.float32)[:T * d].view(T, d)
+        # x in the run's type: float32 runs read the residual stream itself; else the copy the previous
+        # block's last norm made, or (first layer) a copy made now
+        if dtype == torch.float32:
+            x = residual
+        else:
+            kept = getattr(ctx, "residual_copy", None)
+            x = kept[1] if kept is not None and kept[0] is residual else \
+                K.scaled_add_rmsnorm(residual, None, None, None, 1.0, 0.0, dtype)
+        for part, norm, conn in self.sublayers:
+            if part is self.mixer:
+                part.forward(x, y, ctx, cache, state, positions)
+            else:
+                part.forward(x, y, ctx)
+            ctx.settle(y)
+            copy = K.scaled_add_rmsnorm(residual, y, conn.scale, norm.weight, conn.skip_scale, norm.eps,
+                                        None if dtype == torch.float32 else dtype, clear_y=True)
+            x = residual if copy is None else copy
+        ctx.residual_copy = (residual, x)
+
+
 BLOCKS.register("prenorm", PreNormBlock)
 BLOCKS.register("hyper_prenorm", HyperPreNormBlock)
+BLOCKS.register("postnorm", PostNormBlock)
 CONNECTIONS.register("hyper_connection", HyperConnection)
+CONNECTIONS.register("layer_scale", LayerScale)

@@ -1,0 +1,130 @@
+"""Routed experts: a mixture-of-experts feed-forward.
+
+    z = Wr h                         router logits, fp32 (the router's weight is kept in fp32)
+    s = softmax(z)  (or sigmoid(z))  over ALL router outputs
+    c = s + correction               choice scores (``correction``: a stored per-output bias used for choosing only)
+    outputs form ``group_count`` equal groups of neighbours; a group's score is its largest c; only outputs of
+    the ``group_keep`` best groups can be chosen (the others count as minus infinity); the ``top`` largest c win
+    y = sum over the chosen e of s_e * expert_e(h)            (``renormalize``: s_e / sum of the chosen s)
+    expert_e(h) = Wdown_e act(Wup_e h)                        for e < num_experts
+    expert_e(h) = h                                           for the ``identity_experts`` outputs after them
+    y += gate * shared(h),  gate = sigmoid(w_g . h) per token (``shared_size``, ``shared_gate``)
+
+Every constant above is a parameter.  Nothing returns to the host between the router and the result: the
+(token, choice) pairs are sorted by expert on the device, the experts run as two grouped contractions over the
+sorted rows (tiles of 8 rows when a step brings few pairs per expert, larger tiles for prompts), and a last pass
+adds the weighted results in the order the choices were made, so a step can be captured in a CUDA graph and a
+token's result does not depend on the rest of the batch.
+"""
+from __future__ import annotations
+
+import os
+from typing import Any, Callable, Dict, Mapping, Optional
+
+import torch
+
+from ..csrc import kernels as K
+from .base import FeedForward, ParamSpec
+from .linear import STORE_F32, Linear
+from .registry import FEED_FORWARDS
+
+_ACTS = {"none": K.ACT_NONE, "relu2": K.ACT_RELU2, "silu": K.ACT_SILU, "gelu_tanh": K.ACT_GELU_TANH}
+# pairs per expert (on average) up to which the 8-row tiles run; beyond, the larger tiles
+_FEW_PAIRS_PER_EXPERT = int(os.environ.get("DLGO_MOE_FEW_PAIRS", 8))
+
+
+class RoutedExperts(FeedForward):
+    def __init__(self, hidden_size: int, intermediate_size: int, num_experts: int, top: int,
+                 identity_experts: int = 0, group_count: int = 1, group_keep: int = 1, score: str = "softmax",
+                 renormalize: bool = False, correction: bool = False, activation: str = "relu2",
+                 shared_size: Optional[int] = None, shared_gate: bool = False,
+                 names: Optional[Mapping[str, str]] = None):
+        super().__init__(hidden_size=hidden_size, intermediate_size=intermediate_size, num_experts=num_experts, top=top,
+                         identity_experts=identity_experts, group_count=group_count, group_keep=group_keep,
+                         score=score, renormalize=renormalize, correction=correction, activation=activation,
+                         shared_size=shared_size, shared_gate=shared_gate, names=names)
+        self.hidden_size = int(hidden_size)
+        self.intermediate_size = int(intermediate_size)
+        self.num_experts = int(num_experts)
+        self.identity_experts = int(identity_experts)
+        self.n_outputs = self.num_experts + self.identity_experts
+        self.top = int(top)
+        self.group_count, self.group_keep = int(group_count), int(group_keep)
+        if score not in ("softmax", "sigmoid"):
+            raise ValueError(f"score must be 'softmax' or 'sigmoid', got {score!r}")
+        if activation not in _ACTS:
+            raise ValueError(f"activation must be one of {sorted(_ACTS)}, got {activation!r}")
+        if self.n_outputs <= 0 or self.n_outputs % self.group_count or not 0 < self.group_keep <= self.group_count:
+            raise ValueError("the router's outputs must form equal groups of which some are kept")
+        if not 0 < self.top <= self.group_keep * (self.n_outputs // self.group_count):
+            raise ValueError("top must be positive and no more than the kept groups hold")
+        self.sigmoid_scores = score == "sigmoid"
+        self.renormalize = bool(renormalize)
+        self.correction = bool(correction)
+        self.act = _ACTS[activation]
+        self.shared_size = None if shared_size is None else int(shared_size)
+        self.shared_gate = bool(shared_gate) and self.shared_size is not None
+        self.names = {"router": "router.weight", "correction": "router.bias", "expert": "experts.{}.",
+                      "up": "up_proj.weight", "down": "down_proj.weight", "shared_up": "shared.up_proj.weight",
+                      "shared_down": "shared.down_proj.weight", "shared_gate": "shared.gate.weight"}
+        self.names.update(names or {})
+        self.w_router: Optional[torch.Tensor] = None        # fp32 [outputs (+ gate row), hidden]
+        self.b_choice: Optional[torch.Tensor] = None
+        self.w_up: Optional[torch.Tensor] = None            # [experts, ff, hidden]
+        self.w_down: Optional[torch.Tensor] = None          # [experts, hidden, ff]
+        self.shared_up: Optional[Linear] = None
+        self.shared_down: Optional[Linear] = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        n, d, f = self.names, self.hidden_size, self.intermediate_size
+        specs = {n["router"]: ParamSpec((self.n_outputs, d))}
+        if self.correction:
+            specs[n["correction"]] = ParamSpec((self.n_outputs,))
+        for e in range(self.num_experts):
+            p = n["expert"].format(e)
+            specs[p + n["up"]] = ParamSpec((f, d))
+            specs[p + n["down"]] = ParamSpec((d, f))
+        if self.shared_size is not None:
+            specs[n["shared_up"]] = ParamSpec((self.shared_size, d))
+            specs[n["shared_down"]] = ParamSpec((d, self.shared_size))
+            if self.shared_gate:
+                specs[n["shared_gate"]] = ParamSpec((1, d))
+        return specs
+
+    def load(self, get: Callable[[str], torch.Tensor], runtime: Any) -> None:
+        n = self.names
+        rows = [get(n["router"]).to(torch.float32)]
+        if self.shared_gate:
+            rows.append(get(n["shared_gate"]).to(torch.float32).reshape(1, self.hidden_size))
+        self.w_router = torch.cat(rows, dim=0).contiguous()      # routers are 32-bit in every precision
+        if self.correction:
+            self.b_choice = get(n["correction"]).to(torch.float32).contiguous()
+        if self.num_experts:
+            ups = [runtime.compute_copy(get(n["expert"].format(e) + n["up"])) for e in range(self.num_experts)]
+            downs = [runtime.compute_copy(get(n["expert"].format(e) + n["down"])) for e in range(self.num_experts)]
+            self.w_up = torch.stack(ups, dim=0).contiguous()
+            self.w_down = torch.stack(downs, dim=0).contiguous()
+        if self.shared_size is not None:
+            self.shared_up = Linear(get(n["shared_up"]), runtime)
+            self.shared_down = Linear(get(n["shared_down"]), runtime)
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: Any) -> None:
+        T, d = x.shape
+        idx, wt, gate = K.moe_router(x, self.w_router, self.b_choice, self.n_outputs, self.shared_gate, self.top,
+                                     self.group_count, self.group_keep, self.sigmoid_scores, self.renormalize)
+        pair_out = None
+        if self.num_experts:
+            pairs = T * self.top
+            few = pairs <= _FEW_PAIRS_PER_EXPERT * self.num_experts
+            plan = K.moe_plan(idx, self.num_experts, K.MOE_FEW_ROWS if few else K.MOE_TILE_ROWS)
+            hidden = torch.empty((pairs, self.intermediate_size), dtype=x.dtype, device=x.device)
+            K.moe_gemm(plan, x, self.w_up, hidden, self.top, False, self.act)          # rows gathered by token
+            pair_out = torch.empty((pairs, d), dtype=torch.float32, device=x.device)
+            K.moe_gemm(plan, hidden, self.w_down, pair_out, None, True, K.ACT_NONE)    # rows scattered by pair
+        shared = None
+        if self.shared_size is not None:
+            shared = self.shared_down(self.shared_up.bias_act(x, None, self.act), STORE_F32)
+        K.moe_combine(residual, pair_out, x, idx, wt, self.num_experts, shared, gate)
+
+
+FEED_FORWARDS.register("routed_experts", RoutedExperts)

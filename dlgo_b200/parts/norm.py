@@ -12,18 +12,24 @@ from .registry import NORMS
 
 
 class RMSNorm(Norm):
-    def __init__(self, size: int, eps: float):
-        super().__init__(size=size, eps=eps)
+    """``one_plus``: the tensor is stored around zero and the norm multiplies by ``1 + w`` (the sum is made once,
+    in fp32, when the weights are loaded).  ``name``: the tensor's name below the part's prefix."""
+
+    def __init__(self, size: int, eps: float, one_plus: bool = False, name: str = "weight"):
+        super().__init__(size=size, eps=eps, one_plus=one_plus, name=name)
         self.size = int(size)
         self.eps = float(eps)
+        self.one_plus = bool(one_plus)
+        self.name = name
         self.weight: Optional[torch.Tensor] = None
         self.out_dtype: Optional[torch.dtype] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {"weight": ParamSpec((self.size,), "one_plus_normal")}
+        return {self.name: ParamSpec((self.size,), "normal" if self.one_plus else "one_plus_normal")}
 
     def load(self, get: Callable[[str], torch.Tensor], runtime: Any) -> None:
-        self.weight = runtime.compute_copy(get("weight"), torch.float32).contiguous()
+        w = get(self.name).to(torch.float32)
+        self.weight = (w + 1.0 if self.one_plus else w).contiguous()
         self.out_dtype = runtime.dtype
 
     def forward(self, residual: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:

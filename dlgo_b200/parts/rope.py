@@ -80,4 +80,26 @@ class RotaryEmbedding(PositionEncoding):
         self.sin = s.contiguous().to(runtime.device)
 
 
+class RotaryFrequencies(PositionEncoding):
+    """Rotary positions without tables: only the frequencies ``f_i = theta^(-2i/rotary_dim)`` (float64, rounded
+    to float32) are kept; a kernel that rotates forms the angle ``float(position) * f_i`` in fp32 and takes its
+    cosine and sine itself, so no context limit is built in.  Pairs are (i, i + rotary_dim/2)."""
+
+    def __init__(self, head_dim: int, rotary_dim: int, theta: float, scaling: Optional[Dict[str, Any]] = None):
+        super().__init__(head_dim=head_dim, rotary_dim=rotary_dim, theta=theta, scaling=scaling)
+        if rotary_dim % 2 or not 0 < rotary_dim <= head_dim:
+            raise ValueError(f"rotary_dim must be even and in (0, head_dim], got {rotary_dim} for head_dim {head_dim}")
+        self.head_dim = int(head_dim)
+        self.rotary_dim = int(rotary_dim)
+        self.theta = float(theta)
+        self.interleaved = False
+        self.scaling = dict(scaling) if scaling else None
+        self.frequencies: Optional[torch.Tensor] = None
+
+    def prepare(self, runtime: Any) -> None:
+        f = torch.tensor(rotary_frequencies(self.rotary_dim, self.theta, self.scaling), dtype=torch.float64)
+        self.frequencies = f.to(torch.float32).contiguous().to(runtime.device)
+
+
 POSITION_ENCODINGS.register("rotary", RotaryEmbedding)
+POSITION_ENCODINGS.register("rotary_frequencies", RotaryFrequencies)
