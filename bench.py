@@ -354,7 +354,39 @@ def dedutar_pair(size):
     return ded, llama
 
 
-def dedutar_compare(size, batch, steps, warmup, prefill_tokens, profile):
+# --only monolix: the Monolix design beside Llama at equal layer sizes (random weights)
+MONOLIX_SIZES = {
+    # width, heads, kv heads, head size, rotated numbers, experts (+ identity outputs), chosen, expert / shared widths
+    "small": dict(width=1024, heads=16, kv=4, dim=64, rot=32, experts=28, identity=4, top=4, groups=4, keep=2,
+                  ff=512, shared=1024, vocab=32000, layers=4),
+    "1b": dict(width=2048, heads=16, kv=4, dim=128, rot=64, experts=56, identity=8, top=8, groups=8, keep=4,
+               ff=1024, shared=2048, vocab=32000, layers=4),
+    "3b": dict(width=3072, heads=24, kv=8, dim=128, rot=64, experts=60, identity=4, top=6, groups=8, keep=4,
+               ff=1536, shared=3072, vocab=32000, layers=4),
+}
+
+
+def monolix_pair(size):
+    """(Monolix config.json, Llama config.json): layers of keys-as-values attention and routed experts, each with
+    tensors of its own; Llama with as many layers of the same width, heads and head size and a feed-forward with
+    the FLOPs a Monolix token spends (its chosen experts, were none of them an identity, and the shared expert)."""
+    z = MONOLIX_SIZES[size]
+    mixer = {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+             "rot": {"base": 500000.0, "dims": z["rot"]}}
+    mlp = {"kind": "moe", "expert": {"ff": z["ff"]}, "shared": {"ff": z["shared"]},
+           "router": {"experts": z["experts"], "identity": z["identity"], "top": z["top"],
+                      "groups": {"count": z["groups"], "keep": z["keep"]}}}
+    mono = {"architecture": "Monolix", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+            "postln_alpha": 2.0, "layers": [{"type": "attention", "mixer": mixer, "mlp": mlp} for _ in range(z["layers"])]}
+    ff = -(-2 * (z["top"] * z["ff"] + z["shared"]) // 3 // 256) * 256
+    llama = dict(architectures=["LlamaForCausalLM"], hidden_size=z["width"], num_hidden_layers=z["layers"],
+                 intermediate_size=ff, num_attention_heads=z["heads"], num_key_value_heads=z["kv"], head_dim=z["dim"],
+                 vocab_size=z["vocab"], rope_theta=500000.0, rope_scaling=None, rms_norm_eps=1e-5,
+                 max_position_embeddings=8192, tie_word_embeddings=False)
+    return mono, llama
+
+
+def dedutar_compare(size, batch, steps, warmup, prefill_tokens, profile, design="dedutar"):
     """Prefill and decode throughput of both models, and (with `profile`) the time per kernel entry point of
     one prompt step and of decode steps launched one by one."""
     import torch
@@ -362,9 +394,9 @@ def dedutar_compare(size, batch, steps, warmup, prefill_tokens, profile):
     from dlgo_b200.config import config_from_dict
     from dlgo_b200.csrc import kernels
     from dlgo_b200.weights import write_random_model
-    out = {"only": "dedutar", "size": size, "batch": batch, "prefill_tokens": prefill_tokens, "dtype": "bf16",
+    out = {"only": design, "size": size, "batch": batch, "prefill_tokens": prefill_tokens, "dtype": "bf16",
            "data": "synthetic", "models": {}}
-    for name, cfg in zip(("dedutar", "llama"), dedutar_pair(size)):
+    for name, cfg in zip((design, "llama"), monolix_pair(size) if design == "monolix" else dedutar_pair(size)):
         tmp = tempfile.mkdtemp(prefix=f"bench_{name}_")
         try:
             write_random_model(config_from_dict(cfg), 2, tmp, device="cuda")
@@ -460,11 +492,12 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="--only prefill: tokens of the prompt")
     ap.add_argument("--prefill-batch", type=int, default=0,
                     help="--only prefill: a packed batch of that many prompts with lengths from --prompt-range")
-    ap.add_argument("--only", choices=["decode", "prefill", "phases", "sampled", "dedutar"],
-                    help="run one small workload (for profiling) and stop; phases: see phase_stamps(); dedutar: "
-                         "prefill and decode of the Dedutar design beside Llama at equal layer sizes")
+    ap.add_argument("--only", choices=["decode", "prefill", "phases", "sampled", "dedutar", "monolix"],
+                    help="run one small workload (for profiling) and stop; phases: see phase_stamps(); dedutar, "
+                         "monolix: prefill and decode of that design beside Llama at equal layer sizes")
+    ap.add_argument("--monolix-size", default="1b", choices=sorted(MONOLIX_SIZES), help="--only monolix: layer sizes")
     ap.add_argument("--dedutar-size", default="1b", choices=sorted(DEDUTAR_SIZES), help="--only dedutar: layer sizes")
-    ap.add_argument("--kernels", action="store_true", help="--only dedutar: also the time per kernel entry point")
+    ap.add_argument("--kernels", action="store_true", help="--only dedutar / monolix: also the time per kernel entry point")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode kernels one by one (for profiling)")
     a = ap.parse_args()
     if a.impl == "reference":
@@ -483,6 +516,10 @@ def main() -> int:
     warmup = max(a.warmup, 3)
     if a.only == "dedutar":
         print(json.dumps(dedutar_compare(a.dedutar_size, a.batch, a.steps, warmup, a.prefill_tokens, a.kernels)))
+        return 0
+    if a.only == "monolix":
+        print(json.dumps(dedutar_compare(a.monolix_size, a.batch, a.steps, warmup, a.prefill_tokens, a.kernels,
+                                         design="monolix")))
         return 0
     pk = peaks()
     global PROMPT_LEN, PROMPT_RANGE

@@ -46,6 +46,8 @@ def _sm_count(device: torch.device) -> int:
 
 
 class GQAAttention(Mixer):
+    head_multiple = 16      # head sizes this mixer's kernels take
+
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                  window: Optional[int] = None, position_encoding: Optional[str] = "rope",
                  cache_group: str = "full"):
@@ -53,8 +55,8 @@ class GQAAttention(Mixer):
                          scale=scale, window=window, position_encoding=position_encoding, cache_group=cache_group)
         if num_heads % num_kv_heads:
             raise ValueError(f"num_heads ({num_heads}) must be a multiple of num_kv_heads ({num_kv_heads})")
-        if head_dim % 16:
-            raise ValueError(f"head_dim must be a multiple of 16, got {head_dim}")
+        if head_dim % self.head_multiple:
+            raise ValueError(f"head_dim must be a multiple of {self.head_multiple}, got {head_dim}")
         if window is not None and window <= 0:
             raise ValueError(f"window must be positive or None, got {window}")
         self.hidden_size = int(hidden_size)
@@ -248,6 +250,8 @@ class KeysAsValuesAttention(GQAAttention):
     and the key as projected (the value).  The projection's result stays fp32 until bias, norm and rotation are
     done (one kernel, which also appends to the cache); scores, softmax and the weighted sum run in the same
     attention kernels as :class:`GQAAttention`.  ``names``: tensor names below the part's prefix."""
+
+    head_multiple = 8       # (16 bytes of bfloat16: what the general attention kernel reads at a time)
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                  bias: bool = False, head_norm: bool = False, eps: float = 1e-6, window: Optional[int] = None,
