@@ -45,6 +45,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "headnorm_rope": ["headnorm_rope.cu"],
     "postnorm": ["postnorm.cu"],
     "moe": ["moe.cu"],
+    "moe_tc": ["moe_tc.cu"],
 }
 _HEADERS = ["common.cuh", "attention_noalloc.h", "attention_combine.cuh", "attention_decode_tiles.cuh", "tcgen05.cuh"]
 

@@ -596,7 +596,7 @@ def scaled_add_rmsnorm(x: torch.Tensor, y: Optional[torch.Tensor], layer_scale: 
 
 
 # ------------------------------------------------------------------ routed experts
-MOE_FEW_ROWS, MOE_TILE_ROWS = 8, 64          # rows per tile of the two grouped contractions
+MOE_FEW_ROWS, MOE_TILE_ROWS, MOE_TC_ROWS = 8, 64, 128      # rows per tile of the grouped contractions
 
 
 def moe_router(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], n_outputs: int,
@@ -618,11 +618,12 @@ def moe_router(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[tor
     idx = torch.empty((T, top), dtype=torch.int32, device=h.device)
     wt = torch.empty((T, top), dtype=torch.float32, device=h.device)
     gate = torch.empty((T,), dtype=torch.float32, device=h.device) if has_gate else None
+    z = torch.empty((T, rows), dtype=torch.float32, device=h.device)
     st = _lib("moe").dlgo_moe_router(
-        _ptr(h), _i(dtype_code(h.dtype)), _i(h.stride(0)), _ptr(w_router), _ptr(correction), _ptr(idx), _ptr(wt),
-        _ptr(gate), _i(T), _i(d), _i(n_outputs), _i(1 if has_gate else 0), _i(top), _i(groups), _i(keep),
+        _ptr(h), _i(dtype_code(h.dtype)), _i(h.stride(0)), _ptr(w_router), _ptr(correction), _ptr(z), _ptr(idx),
+        _ptr(wt), _ptr(gate), _i(T), _i(d), _i(n_outputs), _i(1 if has_gate else 0), _i(top), _i(groups), _i(keep),
         _i(1 if sigmoid_scores else 0), _i(1 if renormalize else 0), _stream())
-    _check(st, "moe_router")
+    _check(st, "moe_router", 2)
     return idx, wt, gate
 
 
@@ -675,6 +676,47 @@ def moe_gemm(plan: MoEPlan, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
         _ptr(plan.offsets), _ptr(plan.tile_expert), _ptr(plan.tile_row0), _ptr(plan.n_tiles), _i(plan.max_tiles),
         _i(N), _i(Kd), _i(act), _i(1 if out.dtype == torch.float32 else 0), _stream())
     _check(st, "moe_gemm")
+    return out
+
+
+def moe_gemm_tc_takes(dtype: torch.dtype, n: int, k: int) -> bool:
+    """Whether the tensor-core grouped contraction takes a weight [experts, n, k] of this type."""
+    return dtype == torch.bfloat16 and n > 0 and k > 0 and k % 8 == 0
+
+
+def moe_gather_rows(plan: MoEPlan, src: torch.Tensor, div: int) -> torch.Tensor:
+    """Rows of ``src`` in the plan's sorted order: ``dst[r] = src[pair(r) // div]`` for the rows that belong to
+    an expert (the others are left unwritten).  Rows must be a multiple of 16 bytes."""
+    if src.dim() != 2 or src.stride(1) != 1:
+        raise KernelError("moe_gather_rows: src must be 2-D with unit inner stride")
+    if not src.is_cuda:
+        raise KernelError("moe_gather_rows: src must live on the GPU")
+    dst = torch.empty((plan.pairs, src.shape[1]), dtype=src.dtype, device=src.device)
+    n_exp = plan.offsets.numel() - 1
+    st = _lib("moe_tc").dlgo_moe_gather_rows(
+        _ptr(src), _ll(src.stride(0) * src.element_size()), _ptr(dst), _i(src.shape[1] * src.element_size()),
+        _ptr(plan.sorted_pair), _ptr(plan.offsets[n_exp:]), _i(div), _i(plan.pairs), _stream())
+    _check(st, "moe_gather_rows")
+    return dst
+
+
+def moe_gemm_tc(plan: MoEPlan, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, scatter: bool, act: int) -> torch.Tensor:
+    """The grouped contraction on the tensor cores (bfloat16, a plan with tiles of 128 rows): ``a`` holds the rows
+    in sorted order, ``w`` is [experts, N, K]; ``out`` (bfloat16 or fp32) receives row r, or with ``scatter`` row
+    pair(r)."""
+    _need(a, torch.bfloat16, "a")
+    _need(w, torch.bfloat16, "w")
+    if plan.tile_rows != MOE_TC_ROWS or w.dim() != 3 or a.dim() != 2 or out.dim() != 2 or out.stride(1) != 1:
+        raise KernelError("moe_gemm_tc: a plan with tiles of 128 rows, a and out 2-D, w [experts, N, K]")
+    E, N, Kd = w.shape
+    if a.shape[1] != Kd or out.shape[1] != N or out.dtype not in (torch.float32, torch.bfloat16):
+        raise KernelError("moe_gemm_tc: shapes or types do not fit")
+    st = _lib("moe_tc").dlgo_moe_gemm_tc(
+        _ptr(a), _ll(a.shape[0]), _ll(a.stride(0)), _ptr(w), _i(E), _ptr(out), _ll(out.stride(0)),
+        _ptr(plan.sorted_pair if scatter else None), _ptr(plan.offsets), _ptr(plan.tile_expert), _ptr(plan.tile_row0),
+        _ptr(plan.n_tiles), _i(plan.max_tiles), _i(N), _i(Kd), _i(act), _i(1 if out.dtype == torch.float32 else 0),
+        _stream())
+    _check(st, "moe_gemm_tc")
     return out
 
 
@@ -1025,7 +1067,8 @@ def gemm_tc_rope(x: torch.Tensor, w: torch.Tensor, qkv: torch.Tensor, pair_tile:
 
 def check_device_errors() -> None:
     """Raise if a kernel gave up a bounded wait on the device since the last check (synchronises)."""
-    for lib, fn in (("gemm_tc", "dlgo_gemm_tc_error"), ("attention_prefill_tc", "dlgo_attention_tc_error")):
+    for lib, fn in (("gemm_tc", "dlgo_gemm_tc_error"), ("attention_prefill_tc", "dlgo_attention_tc_error"),
+                    ("moe_tc", "dlgo_moe_tc_error")):
         if lib in build._loaded:
             v = getattr(build._loaded[lib], fn)()
             if v != 0:

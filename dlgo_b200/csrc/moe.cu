@@ -36,7 +36,6 @@ __device__ __forceinline__ float apply_act(float v, int act) {
 }
 
 // ------------------------------------------------------------------------------------------ router
-constexpr int RT_TOK = 8;       // tokens of a block = warps of a block
 
 // (value, index) of the largest entry of v[0..n), ties to the lower index; the whole warp takes part
 __device__ __forceinline__ void warp_argmax(const float* v, int n, int lane, float& best, int& at) {
@@ -54,46 +53,102 @@ __device__ __forceinline__ void warp_argmax(const float* v, int n, int lane, flo
   }
 }
 
-template <typename T>
-__global__ void __launch_bounds__(RT_TOK * 32)
-moe_router_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ Wr, const float* __restrict__ corr,
-                  int* __restrict__ idx, float* __restrict__ wt, float* __restrict__ gate, int tokens, int d, int n,
-                  int has_gate, int top, int groups, int keep, int sigmoid_scores, int renormalize) {
+// Router logits z[t][j] = Wr[j] . h[t] in fp32: a warp per pair of outputs, TOK tokens of a block at once (the weight
+// rows are read once per block), lanes along k with 16-byte loads of the fp32 weight.
+constexpr int RL_WARPS = 8, RL_OPW = 2;
+
+template <typename T> struct Quad;
+template <> struct Quad<float> {
+  static __device__ __forceinline__ void load(const float* p, float* o) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+  }
+};
+template <> struct Quad<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* o) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&v);
+    const float2 a = __bfloat1622float2(hh[0]), b = __bfloat1622float2(hh[1]);
+    o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y;
+  }
+};
+
+template <typename T, int TOK, bool VEC>
+__global__ void __launch_bounds__(RL_WARPS * 32)
+moe_logits_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ Wr, float* __restrict__ z, int tokens,
+                  int d, int rows) {
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t0 = blockIdx.x * TOK;
+  const int nt = min(TOK, tokens - t0);
+  const int j0 = (blockIdx.y * RL_WARPS + warp) * RL_OPW;
+  if (j0 >= rows) return;
+  const float* wr[RL_OPW];
+#pragma unroll
+  for (int o = 0; o < RL_OPW; ++o) wr[o] = Wr + (size_t)min(j0 + o, rows - 1) * d;
+  float acc[RL_OPW][TOK];
+#pragma unroll
+  for (int o = 0; o < RL_OPW; ++o)
+#pragma unroll
+    for (int i = 0; i < TOK; ++i) acc[o][i] = 0.f;
+  pdl_wait();
+  if (VEC) {
+    for (int k = lane * 4; k < d; k += 128) {
+      float wv[RL_OPW][4];
+#pragma unroll
+      for (int o = 0; o < RL_OPW; ++o) Quad<float>::load(wr[o] + k, wv[o]);
+#pragma unroll
+      for (int i = 0; i < TOK; ++i) {
+        if (i < nt) {
+          float hv[4];
+          Quad<T>::load(h + (size_t)(t0 + i) * ldh + k, hv);
+#pragma unroll
+          for (int o = 0; o < RL_OPW; ++o)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[o][i] = fmaf(wv[o][c], hv[c], acc[o][i]);
+        }
+      }
+    }
+  } else {
+    for (int k = lane; k < d; k += 32) {
+#pragma unroll
+      for (int i = 0; i < TOK; ++i) {
+        if (i < nt) {
+          const float hv = to_float(h[(size_t)(t0 + i) * ldh + k]);
+#pragma unroll
+          for (int o = 0; o < RL_OPW; ++o) acc[o][i] = fmaf(wr[o][k], hv, acc[o][i]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 0; o < RL_OPW; ++o)
+#pragma unroll
+    for (int i = 0; i < TOK; ++i) {
+      const float sum = warp_sum(acc[o][i]);
+      if (lane == 0 && i < nt && j0 + o < rows) z[(size_t)(t0 + i) * rows + j0 + o] = sum;
+    }
+}
+
+// The choice: a warp per token over its row of logits.
+constexpr int RC_WARPS = 4;
+
+__global__ void __launch_bounds__(RC_WARPS * 32)
+moe_choose_kernel(const float* __restrict__ zg, const float* __restrict__ corr, int* __restrict__ idx,
+                  float* __restrict__ wt, float* __restrict__ gate, int tokens, int n, int has_gate, int top, int groups,
+                  int keep, int sigmoid_scores, int renormalize) {
   extern __shared__ float rt_smem[];
   pdl_launch_dependents();
   const int rows = n + (has_gate ? 1 : 0);
-  float* z = rt_smem;                              // [RT_TOK][rows]
-  float* c = z + (size_t)RT_TOK * rows;            // [RT_TOK][n]
-  float* gs = c + (size_t)RT_TOK * n;              // [RT_TOK][groups]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int t0 = blockIdx.x * RT_TOK;
-  const int nt = min(RT_TOK, tokens - t0);
+  float* zt = rt_smem + (size_t)warp * (rows + n + groups);      // scores
+  float* ct = zt + rows;                                          // choice scores
+  float* gt = ct + n;                                             // group scores
+  const int t = blockIdx.x * RC_WARPS + warp;
   pdl_wait();
-  // router logits: a warp per output, all tokens of the block at once (the weight row is read once)
-  for (int j = warp; j < rows; j += RT_TOK) {
-    const float* wr = Wr + (size_t)j * d;
-    float acc[RT_TOK];
-#pragma unroll
-    for (int i = 0; i < RT_TOK; ++i) acc[i] = 0.f;
-    for (int k = lane; k < d; k += 32) {
-      const float wv = wr[k];
-#pragma unroll
-      for (int i = 0; i < RT_TOK; ++i)
-        if (i < nt) acc[i] = fmaf(wv, to_float(h[(size_t)(t0 + i) * ldh + k]), acc[i]);
-    }
-#pragma unroll
-    for (int i = 0; i < RT_TOK; ++i) {
-      const float s = warp_sum(acc[i]);
-      if (lane == 0) z[(size_t)i * rows + j] = s;
-    }
-  }
-  __syncthreads();
-  if (warp >= nt) return;
-  // choice: a warp per token
-  const int t = t0 + warp;
-  float* zt = z + (size_t)warp * rows;
-  float* ct = c + (size_t)warp * n;
-  float* gt = gs + (size_t)warp * groups;
+  if (t >= tokens) return;
+  for (int j = lane; j < rows; j += 32) zt[j] = zg[(size_t)t * rows + j];
+  __syncwarp();
   if (has_gate && lane == 0) gate[t] = 1.f / (1.f + expf(-zt[n]));
   if (sigmoid_scores) {
     for (int j = lane; j < n; j += 32) zt[j] = 1.f / (1.f + expf(-zt[j]));
@@ -152,10 +207,8 @@ moe_router_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ Wr
     }
     __syncwarp();
   }
-  if (renormalize) {
-    __syncwarp();
+  if (renormalize)
     for (int r = lane; r < top; r += 32) wt[(size_t)t * top + r] /= wsum;
-  }
 }
 
 // -------------------------------------------------------------------------------------------- plan
@@ -408,23 +461,40 @@ moe_combine_kernel(float* __restrict__ y, const float* __restrict__ pair_out, co
 
 using namespace dlgo;
 
-DLGO_EXPORT int dlgo_moe_router(const void* h, int dtype, int ldh, const float* Wr, const float* corr, int* idx, float* wt,
-                                float* gate, int tokens, int d, int n, int has_gate, int top, int groups, int keep,
-                                int sigmoid_scores, int renormalize, cudaStream_t stream) {
+template <typename T>
+static void launch_logits(const void* h, int ldh, const float* Wr, float* z, int tokens, int d, int rows,
+                          cudaStream_t stream) {
+  const bool vec = d % 4 == 0 && ldh % 4 == 0 && ((uintptr_t)h % 16) == 0 && ((uintptr_t)Wr % 16) == 0;
+  const int by = (rows + RL_WARPS * RL_OPW - 1) / (RL_WARPS * RL_OPW);
+  dim3 block(RL_WARPS * 32);
+  if (tokens <= 64) {
+    dim3 grid((tokens + 7) / 8, by);
+    if (vec) launch_kernel(moe_logits_kernel<T, 8, true>, grid, block, 0, stream, (const T*)h, ldh, Wr, z, tokens, d, rows);
+    else launch_kernel(moe_logits_kernel<T, 8, false>, grid, block, 0, stream, (const T*)h, ldh, Wr, z, tokens, d, rows);
+  } else {
+    dim3 grid((tokens + 31) / 32, by);
+    if (vec) launch_kernel(moe_logits_kernel<T, 32, true>, grid, block, 0, stream, (const T*)h, ldh, Wr, z, tokens, d, rows);
+    else launch_kernel(moe_logits_kernel<T, 32, false>, grid, block, 0, stream, (const T*)h, ldh, Wr, z, tokens, d, rows);
+  }
+}
+
+// Two launches: the logits z [tokens, n (+ 1)] (scratch, fp32), then the choice.
+DLGO_EXPORT int dlgo_moe_router(const void* h, int dtype, int ldh, const float* Wr, const float* corr, float* z, int* idx,
+                                float* wt, float* gate, int tokens, int d, int n, int has_gate, int top, int groups,
+                                int keep, int sigmoid_scores, int renormalize, cudaStream_t stream) {
   if (tokens <= 0) return DLGO_OK;
   if (n <= 0 || top <= 0 || top > n || groups <= 0 || n % groups || keep <= 0 || keep > groups || d <= 0)
     return DLGO_ERR_SIZE;
-  const size_t smem = sizeof(float) * RT_TOK * ((size_t)(n + (has_gate ? 1 : 0)) + n + groups);
+  const int rows = n + (has_gate ? 1 : 0);
+  const size_t smem = sizeof(float) * RC_WARPS * ((size_t)rows + n + groups);
   if (smem > 48 * 1024) return DLGO_ERR_SIZE;
-  dim3 grid((tokens + RT_TOK - 1) / RT_TOK), block(RT_TOK * 32);
-  if (dtype == DLGO_F32)
-    launch_kernel(moe_router_kernel<float>, grid, block, smem, stream, (const float*)h, ldh, Wr, corr, idx, wt, gate,
-                  tokens, d, n, has_gate, top, groups, keep, sigmoid_scores, renormalize);
-  else if (dtype == DLGO_BF16)
-    launch_kernel(moe_router_kernel<__nv_bfloat16>, grid, block, smem, stream, (const __nv_bfloat16*)h, ldh, Wr, corr,
-                  idx, wt, gate, tokens, d, n, has_gate, top, groups, keep, sigmoid_scores, renormalize);
-  else
-    return DLGO_ERR_DTYPE;
+  if (dtype == DLGO_F32) launch_logits<float>(h, ldh, Wr, z, tokens, d, rows, stream);
+  else if (dtype == DLGO_BF16) launch_logits<__nv_bfloat16>(h, ldh, Wr, z, tokens, d, rows, stream);
+  else return DLGO_ERR_DTYPE;
+  int st = launch_status();
+  if (st != DLGO_OK) return st;
+  launch_kernel(moe_choose_kernel, dim3((tokens + RC_WARPS - 1) / RC_WARPS), dim3(RC_WARPS * 32), smem, stream,
+                (const float*)z, corr, idx, wt, gate, tokens, n, has_gate, top, groups, keep, sigmoid_scores, renormalize);
   return launch_status();
 }
 

@@ -1,0 +1,302 @@
+// Grouped contraction of routed experts on the tensor cores (tcgen05), for prompts in bfloat16.
+//
+// Rows are (token, choice) pairs sorted by expert (the plan of moe.cu, tiles of 128 rows): tile t belongs to
+// expert e = tile_expert[t] and covers sorted rows row0 .. row0 + 127, of which the first
+// offsets[e + 1] - row0 are the expert's (the rest belong to the next expert, or lie beyond the last pair: they
+// are computed and never stored).
+//
+//   out[o(r)][n] = act( sum_k A[r][k] * W[e][n][k] )
+//
+// A [rows, K] holds the rows in sorted order (moe_gather_rows copies the tokens' rows there for the experts'
+// first contraction; the second reads the first one's output, which is written in sorted order).  W is the
+// experts' weights stacked [experts * N, K].  Both operands arrive by TMA (128-byte swizzle, zero fill beyond
+// the tensors, no multicast) in a shared-memory ring; one thread issues tcgen05.mma into a 128 x BN fp32
+// accumulator in tensor memory; four warps read it back (a lane per row), apply the activation in fp32 and
+// store a row's 32 columns at a time: in the activation type at row r, or fp32 at row o_scatter[r].
+// Warp 0 loads, warp 1 issues MMAs, warps 2-5 are the epilogue.  Every wait is bounded and sets an error word.
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+namespace dlgo {
+
+using namespace sm100;
+
+constexpr int GT_M = 128, GT_K = 64, GT_UMMA_K = 16, GT_THREADS = 192;
+enum { GT_ACT_NONE = 0, GT_ACT_RELU2 = 1, GT_ACT_SILU = 2, GT_ACT_GELU_TANH = 3 };
+
+__device__ int g_moe_tc_error = 0;
+
+struct GroupedTcParams {
+  const int* offsets;
+  const int* tile_expert;
+  const int* tile_row0;
+  const int* n_tiles;
+  const int* o_scatter;     // null: sorted row r is row r of out
+  void* out;
+  long long ldo;
+  int out_f32, act, N, K, stages;
+};
+
+__device__ __forceinline__ float gt_act(float v, int act) {
+  switch (act) {
+    case GT_ACT_RELU2: { const float r = fmaxf(v, 0.f); return r * r; }
+    case GT_ACT_SILU: return v / (1.f + __expf(-v));
+    case GT_ACT_GELU_TANH: return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    default: return v;
+  }
+}
+
+template <int BN>
+__global__ void __launch_bounds__(GT_THREADS)
+moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                   const __grid_constant__ GroupedTcParams p) {
+  constexpr int A_BYTES = GT_M * GT_K * 2, B_BYTES = BN * GT_K * 2, STAGE = A_BYTES + B_BYTES;
+  extern __shared__ uint8_t gt_smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)gt_smem_raw + 1023) & ~(uintptr_t)1023);
+  const int STAGES = p.stages;
+  uint64_t* full = (uint64_t*)(smem + STAGES * STAGE);
+  uint64_t* empty = full + STAGES;
+  uint64_t* accum = empty + STAGES;
+  uint32_t* tmem_slot = (uint32_t*)(accum + 1);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  pdl_wait();                       // the plan and the rows are written by earlier kernels of the step
+  const int tile = blockIdx.y;
+  if (tile >= *p.n_tiles) return;   // before anything is allocated
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int e = p.tile_expert[tile], row0 = p.tile_row0[tile];
+  const int nr = min(GT_M, p.offsets[e + 1] - row0);
+  const int n0 = blockIdx.x * BN;
+  const int nkb = (p.K + GT_K - 1) / GT_K;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(accum, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, BN);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  // Only now may the next kernel of the stream be scheduled: a tensor-core kernel allocates tensor memory in its
+  // prologue and then waits for this grid; were it resident before this CTA holds its own columns, the two could
+  // wait for each other.  (A grid's dependents start once every CTA of it has got here or has left.)
+  pdl_launch_dependents();
+
+  if (warp == 0) {
+    if (elect_one()) {
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % STAGES;
+        const uint32_t ph = (i / STAGES) & 1;
+        if (i >= STAGES && !mbar_wait(&empty[s], ph ^ 1, abort_flag)) break;
+        uint8_t* a_dst = smem + s * STAGE;
+        mbar_expect_tx(&full[s], STAGE);
+        tma_load_2d(a_dst, &map_a, &full[s], i * GT_K, row0);
+        tma_load_2d(a_dst + A_BYTES, &map_b, &full[s], i * GT_K, e * p.N + n0);
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16(GT_M, BN);
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % STAGES;
+        const uint32_t ph = (i / STAGES) & 1;
+        if (!mbar_wait(&full[s], ph, abort_flag)) break;
+        tc_fence_after_sync();
+        const uint32_t a_addr = smem_u32(smem + s * STAGE);
+        const uint64_t da = umma_desc_k_sw128(a_addr);
+        const uint64_t db = umma_desc_k_sw128(a_addr + A_BYTES);
+#pragma unroll
+        for (int k = 0; k < GT_K / GT_UMMA_K; ++k) umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (i | k) != 0);
+        umma_commit(&empty[s]);
+      }
+      umma_commit(accum);
+    }
+  } else {
+    const int quarter = warp & 3;                 // warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31
+    const int r_in = quarter * 32 + lane;
+    const bool ok = mbar_wait(accum, 0, abort_flag);
+    tc_fence_after_sync();
+    const bool mine = ok && r_in < nr;
+    long long dst_row = 0;
+    if (mine) dst_row = p.o_scatter != nullptr ? p.o_scatter[row0 + r_in] : (row0 + r_in);
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+      if (n0 + c0 >= p.N) break;                  // (uniform over the warp)
+      float v[32];
+      if (ok) {
+        tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+        tmem_ld_wait();
+      }
+      if (!mine) continue;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = gt_act(v[j], p.act);
+      const int col = n0 + c0;
+      if (p.out_f32) {
+        float* dst = (float*)p.out + dst_row * p.ldo + col;
+        if (col + 32 <= p.N && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        } else {
+          for (int j = 0; j < 32 && col + j < p.N; ++j) dst[j] = v[j];
+        }
+      } else {
+        __nv_bfloat16* dst = (__nv_bfloat16*)p.out + dst_row * p.ldo + col;
+        if (col + 32 <= p.N && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 o;
+            __nv_bfloat162 b0 = __floats2bfloat162_rn(v[j], v[j + 1]), b1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+            __nv_bfloat162 b2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), b3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+            o.x = *reinterpret_cast<unsigned*>(&b0); o.y = *reinterpret_cast<unsigned*>(&b1);
+            o.z = *reinterpret_cast<unsigned*>(&b2); o.w = *reinterpret_cast<unsigned*>(&b3);
+            *reinterpret_cast<uint4*>(dst + j) = o;
+          }
+        } else {
+          for (int j = 0; j < 32 && col + j < p.N; ++j) dst[j] = __float2bfloat16_rn(v[j]);
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) atomicExch(&g_moe_tc_error, 1);
+    // give tile loads that may still be in flight time to land before shared memory is handed on
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, BN);
+  }
+}
+
+// Rows of the step's tokens in sorted pair order: dst[r] = src[pair(r) / div] for the r < offsets[experts] rows
+// that belong to an expert (16 bytes per thread and step).
+__global__ void __launch_bounds__(256)
+moe_gather_rows_kernel(const uint4* __restrict__ src, long long src_ld16, uint4* __restrict__ dst, int row16,
+                       const int* __restrict__ sorted_pair, const int* __restrict__ total, int div, int max_rows) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int n = min(*total, max_rows);
+  const long long items = (long long)n * row16;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < items; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / row16), c = (int)(i - (long long)r * row16);
+    dst[(long long)r * row16 + c] = src[(long long)(sorted_pair[r] / div) * src_ld16 + c];
+  }
+}
+
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// [rows, K] bf16, row stride ld elements; box = 64 columns x box_rows rows, 128-byte swizzle, zero fill
+int make_map(CUtensorMap* m, const void* base, long long rows, int K, long long ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return DLGO_ERR_DRIVER;
+  if (((uintptr_t)base & 15) != 0 || (ld % 8) != 0) return DLGO_ERR_ALIGN;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)GT_K, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? DLGO_OK : DLGO_ERR_DRIVER;
+}
+
+template <int BN>
+int launch_grouped(const CUtensorMap& ma, const CUtensorMap& mb, GroupedTcParams p, int max_tiles, cudaStream_t stream) {
+  constexpr int STAGE = (GT_M + BN) * GT_K * 2;
+  const int nkb = (p.K + GT_K - 1) / GT_K;
+  // a ring that lets two CTAs share an SM (one's epilogue under the other's MMAs)
+  int stages = (100 * 1024) / STAGE;
+  if (stages > nkb) stages = nkb;
+  if (stages < 2) stages = 2;
+  p.stages = stages;
+  const int smem = stages * STAGE + 1024 + 256;
+  static int configured = 0;
+  if (configured < smem) {
+    cudaError_t e = cudaFuncSetAttribute(moe_gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
+    if (e != cudaSuccess) return (int)e;
+    configured = 110 * 1024;
+  }
+  dim3 grid((p.N + BN - 1) / BN, max_tiles);
+  launch_kernel(moe_gemm_tc_kernel<BN>, grid, dim3(GT_THREADS), (size_t)smem, stream, ma, mb, p);
+  return launch_status();
+}
+
+}  // namespace
+}  // namespace dlgo
+
+using namespace dlgo;
+
+// 1 if the tensor-core kernel takes these sizes (bfloat16 only): 16-byte rows for TMA.
+DLGO_EXPORT int dlgo_moe_gemm_tc_takes(int N, int K) { return (N > 0 && K > 0 && K % 8 == 0) ? 1 : 0; }
+
+// A [a_rows, K] bf16 (row stride lda) in sorted row order; W [experts * N, K] bf16 contiguous; the plan's tiles
+// have 128 rows.  out: bf16 or fp32 (out_f32), row stride ldo, rows r or o_scatter[r].
+DLGO_EXPORT int dlgo_moe_gemm_tc(const void* A, long long a_rows, long long lda, const void* W, int experts, void* out,
+                                 long long ldo, const int* o_scatter, const int* offsets, const int* tile_expert,
+                                 const int* tile_row0, const int* n_tiles, int max_tiles, int N, int K, int act,
+                                 int out_f32, cudaStream_t stream) {
+  if (max_tiles <= 0 || max_tiles > 65535 || a_rows <= 0 || experts <= 0) return DLGO_ERR_SIZE;
+  if (!dlgo_moe_gemm_tc_takes(N, K)) return DLGO_ERR_SIZE;
+  CUtensorMap ma, mb;
+  const int bn = N >= 256 ? 256 : 128;
+  int st = make_map(&ma, A, a_rows, K, lda, GT_M);
+  if (st != DLGO_OK) return st;
+  st = make_map(&mb, W, (long long)experts * N, K, K, bn);
+  if (st != DLGO_OK) return st;
+  GroupedTcParams p{offsets, tile_expert, tile_row0, n_tiles, o_scatter, out, ldo, out_f32, act, N, K, 0};
+  return bn == 256 ? launch_grouped<256>(ma, mb, p, max_tiles, stream) : launch_grouped<128>(ma, mb, p, max_tiles, stream);
+}
+
+// dst[r][:] = src[sorted_pair[r] / div][:] for the rows that belong to an expert; rows of `row_bytes` (a multiple of 16)
+DLGO_EXPORT int dlgo_moe_gather_rows(const void* src, long long src_ld_bytes, void* dst, int row_bytes,
+                                     const int* sorted_pair, const int* total, int div, int max_rows,
+                                     cudaStream_t stream) {
+  if (max_rows <= 0) return DLGO_OK;
+  if (row_bytes <= 0 || row_bytes % 16 || src_ld_bytes % 16 || div <= 0 || ((uintptr_t)src & 15) || ((uintptr_t)dst & 15))
+    return DLGO_ERR_ALIGN;
+  const long long items = (long long)max_rows * (row_bytes / 16);
+  long long want = (items + 255) / 256;
+  const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+  launch_kernel(moe_gather_rows_kernel, dim3(blocks), dim3(256), 0, stream, (const uint4*)src, src_ld_bytes / 16,
+                (uint4*)dst, row_bytes / 16, sorted_pair, total, div, max_rows);
+  return launch_status();
+}
+
+// The error word (1: a bounded wait ran out), cleared by the read.
+DLGO_EXPORT int dlgo_moe_tc_error() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, dlgo::g_moe_tc_error, sizeof(int)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(dlgo::g_moe_tc_error, &zero, sizeof(int));
+  return v;
+}

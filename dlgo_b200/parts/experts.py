@@ -31,6 +31,7 @@ from .registry import FEED_FORWARDS
 _ACTS = {"none": K.ACT_NONE, "relu2": K.ACT_RELU2, "silu": K.ACT_SILU, "gelu_tanh": K.ACT_GELU_TANH}
 # pairs per expert (on average) up to which the 8-row tiles run; beyond, the larger tiles
 _FEW_PAIRS_PER_EXPERT = int(os.environ.get("DLGO_MOE_FEW_PAIRS", 8))
+_TENSOR_CORES = os.environ.get("DLGO_MOE_TC", "1") != "0"       # 0: the fp32-pipe tiles also in bfloat16
 
 
 class RoutedExperts(FeedForward):
@@ -74,6 +75,7 @@ class RoutedExperts(FeedForward):
         self.w_down: Optional[torch.Tensor] = None          # [experts, hidden, ff]
         self.shared_up: Optional[Linear] = None
         self.shared_down: Optional[Linear] = None
+        self.on_tensor_cores = False
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         n, d, f = self.names, self.hidden_size, self.intermediate_size
@@ -104,6 +106,9 @@ class RoutedExperts(FeedForward):
             downs = [runtime.compute_copy(get(n["expert"].format(e) + n["down"])) for e in range(self.num_experts)]
             self.w_up = torch.stack(ups, dim=0).contiguous()
             self.w_down = torch.stack(downs, dim=0).contiguous()
+            self.on_tensor_cores = (_TENSOR_CORES and
+                                    K.moe_gemm_tc_takes(self.w_up.dtype, self.intermediate_size, self.hidden_size) and
+                                    K.moe_gemm_tc_takes(self.w_down.dtype, self.hidden_size, self.intermediate_size))
         if self.shared_size is not None:
             self.shared_up = Linear(get(n["shared_up"]), runtime)
             self.shared_down = Linear(get(n["shared_down"]), runtime)
@@ -116,11 +121,18 @@ class RoutedExperts(FeedForward):
         if self.num_experts:
             pairs = T * self.top
             few = pairs <= _FEW_PAIRS_PER_EXPERT * self.num_experts
-            plan = K.moe_plan(idx, self.num_experts, K.MOE_FEW_ROWS if few else K.MOE_TILE_ROWS)
             hidden = torch.empty((pairs, self.intermediate_size), dtype=x.dtype, device=x.device)
-            K.moe_gemm(plan, x, self.w_up, hidden, self.top, False, self.act)          # rows gathered by token
             pair_out = torch.empty((pairs, d), dtype=torch.float32, device=x.device)
-            K.moe_gemm(plan, hidden, self.w_down, pair_out, None, True, K.ACT_NONE)    # rows scattered by pair
+            if not few and self.on_tensor_cores:
+                # prompts in bfloat16: the tokens' rows copied into sorted order, then both contractions on tcgen05
+                plan = K.moe_plan(idx, self.num_experts, K.MOE_TC_ROWS)
+                rows = K.moe_gather_rows(plan, x, self.top)
+                K.moe_gemm_tc(plan, rows, self.w_up, hidden, False, self.act)
+                K.moe_gemm_tc(plan, hidden, self.w_down, pair_out, True, K.ACT_NONE)
+            else:
+                plan = K.moe_plan(idx, self.num_experts, K.MOE_FEW_ROWS if few else K.MOE_TILE_ROWS)
+                K.moe_gemm(plan, x, self.w_up, hidden, self.top, False, self.act)          # rows gathered by token
+                K.moe_gemm(plan, hidden, self.w_down, pair_out, None, True, K.ACT_NONE)    # rows scattered by pair
         shared = None
         if self.shared_size is not None:
             shared = self.shared_down(self.shared_up.bias_act(x, None, self.act), STORE_F32)

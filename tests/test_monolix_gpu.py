@@ -200,6 +200,47 @@ def test_experts_grouped_contractions(T, d, ff, E, ident, top, dtype):
         assert torch.allclose(y.cpu().double(), ref, rtol=tol, atol=tol * float(ref.abs().max())), (rows, float((y.cpu().double() - ref).abs().max()))
 
 
+@pytest.mark.parametrize("T", [3, 130, 700])
+@pytest.mark.parametrize("d, ff, E, ident, top", [(256, 192, 5, 1, 3), (128, 96, 12, 4, 4), (72, 40, 3, 0, 2), (512, 320, 2, 0, 1)])
+def test_experts_on_the_tensor_cores(T, d, ff, E, ident, top):
+    """The grouped contraction on tcgen05 (tiles of 128 sorted rows; an expert's last tile runs into the next
+    expert's rows, a weight tile into the next expert's weight: neither may be stored) against the fp32-pipe
+    tiles, which the test above checks against a loop over tokens."""
+    from dlgo_b200.csrc import kernels as K
+    g = torch.Generator().manual_seed(T + d)
+    n = E + ident
+    h = torch.randn(T, d, generator=g).to(torch.bfloat16).to(DEV)
+    up = (torch.randn(E, ff, d, generator=g) / d ** 0.5).to(torch.bfloat16).to(DEV)
+    down = (torch.randn(E, d, ff, generator=g) / ff ** 0.5).to(torch.bfloat16).to(DEV)
+    idx = torch.stack([torch.randperm(n, generator=g)[:top] for _ in range(T)]).to(torch.int32)
+    if T > 100:
+        idx[: T // 2, 0] = 0                                   # one expert with many tiles, some with few rows
+    idx = idx.to(DEV)
+    assert K.moe_gemm_tc_takes(torch.bfloat16, ff, d) and K.moe_gemm_tc_takes(torch.bfloat16, d, ff)
+    ref_plan = K.moe_plan(idx, E, K.MOE_TILE_ROWS)
+    hid_ref = torch.zeros(T * top, ff, dtype=torch.bfloat16, device=DEV)
+    K.moe_gemm(ref_plan, h, up, hid_ref, top, False, K.ACT_RELU2)
+    out_ref = torch.zeros(T * top, d, device=DEV)
+    K.moe_gemm(ref_plan, hid_ref, down, out_ref, None, True, K.ACT_NONE)
+    plan = K.moe_plan(idx, E, K.MOE_TC_ROWS)
+    rows = K.moe_gather_rows(plan, h, top)
+    hid = torch.full((T * top, ff), float("nan"), dtype=torch.bfloat16, device=DEV)
+    K.moe_gemm_tc(plan, rows, up, hid, False, K.ACT_RELU2)
+    out = torch.zeros(T * top, d, device=DEV)
+    K.moe_gemm_tc(plan, hid, down, out, True, K.ACT_NONE)
+    K.check_device_errors()
+    total = int(plan.offsets[-1])
+    assert total == int((idx < E).sum())
+    # sorted rows of the two plans differ in order within an expert: compare through the pair numbers
+    a = torch.zeros(T * top, ff, device=DEV)
+    a[plan.sorted_pair[:total].long()] = hid[:total].float()
+    b = torch.zeros(T * top, ff, device=DEV)
+    b[ref_plan.sorted_pair[:total].long()] = hid_ref[:total].float()
+    assert torch.isfinite(hid[:total].float()).all()
+    assert torch.allclose(a, b, rtol=2e-2, atol=2e-2 * float(b.abs().max()))
+    assert torch.allclose(out, out_ref, rtol=3e-2, atol=3e-2 * float(out_ref.abs().max())), float((out - out_ref).abs().max())
+
+
 # ---------------------------------------------- one layer: a key that carries the answer
 def one_layer(mixer, mlp=None, width=48, vocab=60, alpha=1.0):
     return {"architecture": "Monolix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "postln_alpha": alpha,
