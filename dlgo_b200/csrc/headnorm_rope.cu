@@ -63,12 +63,13 @@ headnorm_rope_append_kernel(float* __restrict__ proj, int ld, const float* __res
   float ss = 0.f;
   for (int i = lane; i < hd; i += 32) {
     float x = src[i];
-    if (clear) src[i] = 0.f;
     if (bias != nullptr) x += bias[(size_t)head * hd + i];
     u[i] = x;
     ss += x * x;
     if (is_k && v_from_k && vdst != nullptr) vdst[i] = from_float<T>(x);
   }
+  if (clear)                     // (after every load of the row has been issued: a store right behind a load holds the loads up)
+    for (int i = lane; i < hd; i += 32) src[i] = 0.f;
   if (!is_q && !is_k) {          // a value head of its own: stored as projected
     if (vdst != nullptr)
       for (int i = lane; i < hd; i += 32) vdst[i] = from_float<T>(u[i]);

@@ -724,7 +724,7 @@ def moe_combine(y: torch.Tensor, pair_out: Optional[torch.Tensor], h: torch.Tens
                 wt: torch.Tensor, n_experts: int, shared: Optional[torch.Tensor] = None,
                 gate: Optional[torch.Tensor] = None) -> None:
     """``y[t] += sum_k wt[t, k] * (pair_out[t * top + k] if idx[t, k] < n_experts else h[t]) + gate[t] * shared[t]``
-    (fp32; ``gate`` None: 1)."""
+    (sums in fp32; ``gate`` None: 1; ``pair_out`` fp32 or of ``h``'s type)."""
     _need(y, torch.float32, "y")
     _need(idx, torch.int32, "idx")
     _need(wt, torch.float32, "wt")
@@ -733,7 +733,9 @@ def moe_combine(y: torch.Tensor, pair_out: Optional[torch.Tensor], h: torch.Tens
     if h.dim() != 2 or h.stride(1) != 1 or tuple(h.shape) != (T, d):
         raise KernelError("moe_combine: h must be [T, d] with unit inner stride")
     if pair_out is not None:
-        _need(pair_out, torch.float32, "pair_out")
+        _need(pair_out, None, "pair_out")
+        if pair_out.dtype not in (torch.float32, h.dtype):
+            raise KernelError("moe_combine: pair_out must be float32 or of h's type")
         if tuple(pair_out.shape) != (T * top, d):
             raise KernelError("moe_combine: pair_out must be [T * top, d]")
     elif n_experts > 0:
@@ -741,7 +743,9 @@ def moe_combine(y: torch.Tensor, pair_out: Optional[torch.Tensor], h: torch.Tens
     for n, t in (("shared", shared), ("gate", gate)):
         if t is not None:
             _need(t, torch.float32, n)
-    st = _lib("moe").dlgo_moe_combine(_ptr(y), _ptr(pair_out), _ptr(h), _i(dtype_code(h.dtype)), _i(h.stride(0)),
+    st = _lib("moe").dlgo_moe_combine(_ptr(y), _ptr(pair_out),
+                                      _i(1 if pair_out is None or pair_out.dtype == torch.float32 else 0), _ptr(h),
+                                      _i(dtype_code(h.dtype)), _i(h.stride(0)),
                                       _ptr(idx), _ptr(wt), _ptr(shared), _ptr(gate), _i(T), _i(d), _i(top),
                                       _i(n_experts), _stream())
     _check(st, "moe_combine")

@@ -53,9 +53,10 @@ __device__ __forceinline__ void warp_argmax(const float* v, int n, int lane, flo
   }
 }
 
-// Router logits z[t][j] = Wr[j] . h[t] in fp32: a warp per pair of outputs, TOK tokens of a block at once (the weight
-// rows are read once per block), lanes along k with 16-byte loads of the fp32 weight.
-constexpr int RL_WARPS = 8, RL_OPW = 2;
+// Router logits z[t][j] = Wr[j] . h[t] in fp32.  A block takes TOK tokens and RL_OB outputs; its eight warps share
+// the k range (chunks of 128 dealt round-robin, 16-byte loads of the fp32 weight), so that even a single token's
+// logits are a few loads deep; the warps' sums meet in shared memory in warp order.
+constexpr int RL_WARPS = 8, RL_OB = 4;
 
 template <typename T> struct Quad;
 template <> struct Quad<float> {
@@ -77,57 +78,68 @@ template <typename T, int TOK, bool VEC>
 __global__ void __launch_bounds__(RL_WARPS * 32)
 moe_logits_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ Wr, float* __restrict__ z, int tokens,
                   int d, int rows) {
+  __shared__ float part[RL_WARPS][RL_OB * TOK];
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int t0 = blockIdx.x * TOK;
   const int nt = min(TOK, tokens - t0);
-  const int j0 = (blockIdx.y * RL_WARPS + warp) * RL_OPW;
-  if (j0 >= rows) return;
-  const float* wr[RL_OPW];
+  const int j0 = blockIdx.y * RL_OB;
+  // rows beyond the last output or token stand in as the last one (their sums are never stored), so that no
+  // load sits behind a branch and a whole iteration's loads are in flight together
+  const float* wr[RL_OB];
 #pragma unroll
-  for (int o = 0; o < RL_OPW; ++o) wr[o] = Wr + (size_t)min(j0 + o, rows - 1) * d;
-  float acc[RL_OPW][TOK];
+  for (int o = 0; o < RL_OB; ++o) wr[o] = Wr + (size_t)min(j0 + o, rows - 1) * d;
+  const T* hrow[TOK];
 #pragma unroll
-  for (int o = 0; o < RL_OPW; ++o)
+  for (int i = 0; i < TOK; ++i) hrow[i] = h + (size_t)(t0 + min(i, nt - 1)) * ldh;
+  float acc[RL_OB][TOK];
+#pragma unroll
+  for (int o = 0; o < RL_OB; ++o)
 #pragma unroll
     for (int i = 0; i < TOK; ++i) acc[o][i] = 0.f;
   pdl_wait();
   if (VEC) {
-    for (int k = lane * 4; k < d; k += 128) {
-      float wv[RL_OPW][4];
+    for (int k = warp * 128 + lane * 4; k < d; k += RL_WARPS * 128) {
+      float wv[RL_OB][4], hv[TOK][4];
 #pragma unroll
-      for (int o = 0; o < RL_OPW; ++o) Quad<float>::load(wr[o] + k, wv[o]);
+      for (int o = 0; o < RL_OB; ++o) Quad<float>::load(wr[o] + k, wv[o]);
 #pragma unroll
-      for (int i = 0; i < TOK; ++i) {
-        if (i < nt) {
-          float hv[4];
-          Quad<T>::load(h + (size_t)(t0 + i) * ldh + k, hv);
+      for (int i = 0; i < TOK; ++i) Quad<T>::load(hrow[i] + k, hv[i]);
 #pragma unroll
-          for (int o = 0; o < RL_OPW; ++o)
+      for (int i = 0; i < TOK; ++i)
 #pragma unroll
-            for (int c = 0; c < 4; ++c) acc[o][i] = fmaf(wv[o][c], hv[c], acc[o][i]);
-        }
-      }
+        for (int o = 0; o < RL_OB; ++o)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) acc[o][i] = fmaf(wv[o][c], hv[i][c], acc[o][i]);
     }
   } else {
-    for (int k = lane; k < d; k += 32) {
+    for (int k = warp * 32 + lane; k < d; k += RL_WARPS * 32) {
+      float wv[RL_OB], hv[TOK];
 #pragma unroll
-      for (int i = 0; i < TOK; ++i) {
-        if (i < nt) {
-          const float hv = to_float(h[(size_t)(t0 + i) * ldh + k]);
+      for (int o = 0; o < RL_OB; ++o) wv[o] = wr[o][k];
 #pragma unroll
-          for (int o = 0; o < RL_OPW; ++o) acc[o][i] = fmaf(wr[o][k], hv, acc[o][i]);
-        }
-      }
+      for (int i = 0; i < TOK; ++i) hv[i] = to_float(hrow[i][k]);
+#pragma unroll
+      for (int i = 0; i < TOK; ++i)
+#pragma unroll
+        for (int o = 0; o < RL_OB; ++o) acc[o][i] = fmaf(wv[o], hv[i], acc[o][i]);
     }
   }
 #pragma unroll
-  for (int o = 0; o < RL_OPW; ++o)
+  for (int o = 0; o < RL_OB; ++o)
 #pragma unroll
     for (int i = 0; i < TOK; ++i) {
       const float sum = warp_sum(acc[o][i]);
-      if (lane == 0 && i < nt && j0 + o < rows) z[(size_t)(t0 + i) * rows + j0 + o] = sum;
+      if (lane == 0) part[warp][o * TOK + i] = sum;
     }
+  __syncthreads();
+  if (threadIdx.x < RL_OB * TOK) {
+    const int o = threadIdx.x / TOK, i = threadIdx.x % TOK;
+    float sum = 0.f;
+#pragma unroll
+    for (int w = 0; w < RL_WARPS; ++w) sum += part[w][threadIdx.x];
+    if (i < nt && j0 + o < rows) z[(size_t)(t0 + i) * rows + j0 + o] = sum;
+  }
 }
 
 // The choice: a warp per token over its row of logits.
@@ -433,28 +445,68 @@ moe_gemm_tiles_kernel(GroupedArgs g) {
 }
 
 // ----------------------------------------------------------------------------------------- combine
-template <typename T>
+// A thread per token and four neighbouring channels (16-byte accesses where rows allow); P is the type of the
+// experts' results (fp32 or the run's type).
+template <typename T, typename P, bool VEC>
 __global__ void __launch_bounds__(256)
-moe_combine_kernel(float* __restrict__ y, const float* __restrict__ pair_out, const T* __restrict__ h, int ldh,
+moe_combine_kernel(float* __restrict__ y, const P* __restrict__ pair_out, const T* __restrict__ h, int ldh,
                    const int* __restrict__ idx, const float* __restrict__ wt, const float* __restrict__ shared,
-                   const float* __restrict__ gate, int tokens, int d, int top, int n_experts, int warp_rows) {
+                   const float* __restrict__ gate, int tokens, int d, int top, int n_experts) {
   pdl_launch_dependents();
-  const int t = warp_rows ? blockIdx.x * 8 + (threadIdx.x >> 5) : blockIdx.x;
-  const int tid = warp_rows ? (threadIdx.x & 31) : threadIdx.x;
-  const int step = warp_rows ? 32 : blockDim.x;
+  constexpr int W = VEC ? 4 : 1;
+  const int per_row = (d + W - 1) / W;
+  const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   pdl_wait();
-  if (t >= tokens) return;
-  const float gt = (shared != nullptr && gate != nullptr) ? gate[t] : 1.f;
-  for (int i = tid; i < d; i += step) {
-    float acc = 0.f;
-    for (int k = 0; k < top; ++k) {
-      const int e = idx[(size_t)t * top + k];
-      const float v = (e < n_experts) ? pair_out[((size_t)t * top + k) * d + i] : to_float(h[(size_t)t * ldh + i]);
-      acc = fmaf(wt[(size_t)t * top + k], v, acc);
+  if (item >= (long long)tokens * per_row) return;
+  const int t = (int)(item / per_row), i = (int)(item - (long long)t * per_row) * W;
+  float acc[W];
+#pragma unroll
+  for (int c = 0; c < W; ++c) acc[c] = 0.f;
+  for (int k = 0; k < top; ++k) {
+    const int e = idx[(size_t)t * top + k];
+    const float wk = wt[(size_t)t * top + k];
+    float v[W];
+    if (e < n_experts) {
+      const P* src = pair_out + ((size_t)t * top + k) * d + i;
+      if (VEC) Quad<P>::load(src, v); else v[0] = to_float(src[0]);
+    } else {
+      const T* src = h + (size_t)t * ldh + i;
+      if (VEC) Quad<T>::load(src, v); else v[0] = to_float(src[0]);
     }
-    if (shared != nullptr) acc = fmaf(gt, shared[(size_t)t * d + i], acc);
-    y[(size_t)t * d + i] += acc;
+#pragma unroll
+    for (int c = 0; c < W; ++c) acc[c] = fmaf(wk, v[c], acc[c]);
   }
+  if (shared != nullptr) {
+    const float gt = gate != nullptr ? gate[t] : 1.f;
+    float v[W];
+    if (VEC) Quad<float>::load(shared + (size_t)t * d + i, v); else v[0] = shared[(size_t)t * d + i];
+#pragma unroll
+    for (int c = 0; c < W; ++c) acc[c] = fmaf(gt, v[c], acc[c]);
+  }
+  float* yr = y + (size_t)t * d + i;
+  if (VEC) {
+    float4 o = *reinterpret_cast<float4*>(yr);
+    o.x += acc[0]; o.y += acc[1]; o.z += acc[2]; o.w += acc[3];
+    *reinterpret_cast<float4*>(yr) = o;
+  } else {
+    yr[0] += acc[0];
+  }
+}
+
+template <typename T, typename P>
+static void launch_combine(float* y, const void* pair_out, const void* h, int ldh, const int* idx, const float* wt,
+                           const float* shared, const float* gate, int tokens, int d, int top, int n_experts,
+                           cudaStream_t stream) {
+  const bool vec = d % 4 == 0 && ldh % 4 == 0 && ((uintptr_t)y % 16) == 0 && ((uintptr_t)pair_out % 16) == 0 &&
+                   ((uintptr_t)h % 16) == 0 && ((uintptr_t)shared % 16) == 0;
+  const long long items = (long long)tokens * (vec ? d / 4 : d);
+  dim3 grid((unsigned)((items + 255) / 256)), block(256);
+  if (vec)
+    launch_kernel(moe_combine_kernel<T, P, true>, grid, block, 0, stream, y, (const P*)pair_out, (const T*)h, ldh, idx,
+                  wt, shared, gate, tokens, d, top, n_experts);
+  else
+    launch_kernel(moe_combine_kernel<T, P, false>, grid, block, 0, stream, y, (const P*)pair_out, (const T*)h, ldh, idx,
+                  wt, shared, gate, tokens, d, top, n_experts);
 }
 
 }  // namespace dlgo
@@ -465,16 +517,16 @@ template <typename T>
 static void launch_logits(const void* h, int ldh, const float* Wr, float* z, int tokens, int d, int rows,
                           cudaStream_t stream) {
   const bool vec = d % 4 == 0 && ldh % 4 == 0 && ((uintptr_t)h % 16) == 0 && ((uintptr_t)Wr % 16) == 0;
-  const int by = (rows + RL_WARPS * RL_OPW - 1) / (RL_WARPS * RL_OPW);
+  const int by = (rows + RL_OB - 1) / RL_OB;
   dim3 block(RL_WARPS * 32);
   if (tokens <= 64) {
     dim3 grid((tokens + 7) / 8, by);
     if (vec) launch_kernel(moe_logits_kernel<T, 8, true>, grid, block, 0, stream, (const T*)h, ldh, Wr, z, tokens, d, rows);
     else launch_kernel(moe_logits_kernel<T, 8, false>, grid, block, 0, stream, (const T*)h, ldh, Wr, z, tokens, d, rows);
   } else {
-    dim3 grid((tokens + 31) / 32, by);
-    if (vec) launch_kernel(moe_logits_kernel<T, 32, true>, grid, block, 0, stream, (const T*)h, ldh, Wr, z, tokens, d, rows);
-    else launch_kernel(moe_logits_kernel<T, 32, false>, grid, block, 0, stream, (const T*)h, ldh, Wr, z, tokens, d, rows);
+    dim3 grid((tokens + 15) / 16, by);
+    if (vec) launch_kernel(moe_logits_kernel<T, 16, true>, grid, block, 0, stream, (const T*)h, ldh, Wr, z, tokens, d, rows);
+    else launch_kernel(moe_logits_kernel<T, 16, false>, grid, block, 0, stream, (const T*)h, ldh, Wr, z, tokens, d, rows);
   }
 }
 
@@ -541,19 +593,19 @@ DLGO_EXPORT int dlgo_moe_gemm(int kind, int dtype, const void* A, long long lda,
   return launch_status();
 }
 
-DLGO_EXPORT int dlgo_moe_combine(float* y, const float* pair_out, const void* h, int dtype, int ldh, const int* idx,
-                                 const float* wt, const float* shared, const float* gate, int tokens, int d, int top,
-                                 int n_experts, cudaStream_t stream) {
+// pair_out: the experts' results [tokens * top, d], fp32 (pair_f32) or of h's type
+DLGO_EXPORT int dlgo_moe_combine(float* y, const void* pair_out, int pair_f32, const void* h, int dtype, int ldh,
+                                 const int* idx, const float* wt, const float* shared, const float* gate, int tokens,
+                                 int d, int top, int n_experts, cudaStream_t stream) {
   if (tokens <= 0) return DLGO_OK;
   if (d <= 0 || top <= 0) return DLGO_ERR_SIZE;
-  const int warp_rows = tokens > 64 && d <= 1024;
-  dim3 grid(warp_rows ? (tokens + 7) / 8 : tokens), block(256);
   if (dtype == DLGO_F32)
-    launch_kernel(moe_combine_kernel<float>, grid, block, 0, stream, y, pair_out, (const float*)h, ldh, idx, wt, shared,
-                  gate, tokens, d, top, n_experts, warp_rows);
+    launch_combine<float, float>(y, pair_out, h, ldh, idx, wt, shared, gate, tokens, d, top, n_experts, stream);
+  else if (dtype == DLGO_BF16 && pair_f32)
+    launch_combine<__nv_bfloat16, float>(y, pair_out, h, ldh, idx, wt, shared, gate, tokens, d, top, n_experts, stream);
   else if (dtype == DLGO_BF16)
-    launch_kernel(moe_combine_kernel<__nv_bfloat16>, grid, block, 0, stream, y, pair_out, (const __nv_bfloat16*)h, ldh,
-                  idx, wt, shared, gate, tokens, d, top, n_experts, warp_rows);
+    launch_combine<__nv_bfloat16, __nv_bfloat16>(y, pair_out, h, ldh, idx, wt, shared, gate, tokens, d, top, n_experts,
+                                                 stream);
   else
     return DLGO_ERR_DTYPE;
   return launch_status();

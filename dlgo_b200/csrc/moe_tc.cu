@@ -127,44 +127,72 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     const int r_in = quarter * 32 + lane;
     const bool ok = mbar_wait(accum, 0, abort_flag);
     tc_fence_after_sync();
-    const bool mine = ok && r_in < nr;
-    long long dst_row = 0;
-    if (mine) dst_row = p.o_scatter != nullptr ? p.o_scatter[row0 + r_in] : (row0 + r_in);
+    // The ring is idle by now (every MMA has read it): each epilogue warp lays 64 columns of its 32 rows out in
+    // its own corner of it, then writes them row by row, so that a store instruction covers whole 128-byte lines
+    // of a few rows instead of 16 bytes of each of 32 rows.
+    constexpr int LD = 68;                                   // floats per staged row (64 + 4: rows shift by 4 banks)
+    float* stg = (float*)smem + quarter * (32 * LD);
+    const int rows_w = min(32, max(0, nr - quarter * 32));   // rows of this warp that belong to the expert
+    long long my_dst = 0;
+    if (ok && lane < rows_w) my_dst = (p.o_scatter != nullptr ? p.o_scatter[row0 + r_in] : (row0 + r_in)) * p.ldo;
+    if (ok && rows_w > 0) {
 #pragma unroll 1
-    for (int c0 = 0; c0 < BN; c0 += 32) {
-      if (n0 + c0 >= p.N) break;                  // (uniform over the warp)
-      float v[32];
-      if (ok) {
-        tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
-        tmem_ld_wait();
-      }
-      if (!mine) continue;
+      for (int c0 = 0; c0 < BN && n0 + c0 < p.N; c0 += 64) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = gt_act(v[j], p.act);
-      const int col = n0 + c0;
-      if (p.out_f32) {
-        float* dst = (float*)p.out + dst_row * p.ldo + col;
-        if (col + 32 <= p.N && ((uintptr_t)dst & 15) == 0) {
+        for (int half = 0; half < 2; ++half) {
+          if (n0 + c0 + half * 32 < p.N) {                   // (uniform over the warp)
+            float v[32];
+            tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c0 + half * 32), v);
+            tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-        } else {
-          for (int j = 0; j < 32 && col + j < p.N; ++j) dst[j] = v[j];
+            for (int j = 0; j < 32; j += 4)
+              *reinterpret_cast<float4*>(stg + lane * LD + half * 32 + j) =
+                  make_float4(gt_act(v[j], p.act), gt_act(v[j + 1], p.act), gt_act(v[j + 2], p.act), gt_act(v[j + 3], p.act));
+          }
         }
-      } else {
-        __nv_bfloat16* dst = (__nv_bfloat16*)p.out + dst_row * p.ldo + col;
-        if (col + 32 <= p.N && ((uintptr_t)dst & 15) == 0) {
-#pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            uint4 o;
-            __nv_bfloat162 b0 = __floats2bfloat162_rn(v[j], v[j + 1]), b1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-            __nv_bfloat162 b2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), b3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-            o.x = *reinterpret_cast<unsigned*>(&b0); o.y = *reinterpret_cast<unsigned*>(&b1);
-            o.z = *reinterpret_cast<unsigned*>(&b2); o.w = *reinterpret_cast<unsigned*>(&b3);
-            *reinterpret_cast<uint4*>(dst + j) = o;
+        __syncwarp();
+        const int col = n0 + c0;
+        const int ncols = min(64, p.N - col);
+        if (p.out_f32) {
+          const int sub = (lane & 15) * 4, rr = lane >> 4;   // 16 lanes a row, two rows an instruction
+#pragma unroll 1
+          for (int r = 0; r < 32; r += 2) {
+            const long long base = __shfl_sync(0xffffffffu, my_dst, r + rr);
+            if (r + rr < rows_w && sub < ncols) {
+              const float4 o = *reinterpret_cast<const float4*>(stg + (r + rr) * LD + sub);
+              float* dst = (float*)p.out + base + col + sub;
+              if (sub + 4 <= ncols && ((uintptr_t)dst & 15) == 0) {
+                *reinterpret_cast<float4*>(dst) = o;
+              } else {
+                const float e[4] = {o.x, o.y, o.z, o.w};
+                for (int j = 0; j < 4 && sub + j < ncols; ++j) dst[j] = e[j];
+              }
+            }
           }
         } else {
-          for (int j = 0; j < 32 && col + j < p.N; ++j) dst[j] = __float2bfloat16_rn(v[j]);
+          const int sub = (lane & 7) * 8, rr = lane >> 3;    // 8 lanes a row, four rows an instruction
+#pragma unroll 1
+          for (int r = 0; r < 32; r += 4) {
+            const long long base = __shfl_sync(0xffffffffu, my_dst, r + rr);
+            if (r + rr < rows_w && sub < ncols) {
+              const float4 a = *reinterpret_cast<const float4*>(stg + (r + rr) * LD + sub);
+              const float4 b = *reinterpret_cast<const float4*>(stg + (r + rr) * LD + sub + 4);
+              __nv_bfloat16* dst = (__nv_bfloat16*)p.out + base + col + sub;
+              if (sub + 8 <= ncols && ((uintptr_t)dst & 15) == 0) {
+                uint4 o;
+                __nv_bfloat162 b0 = __floats2bfloat162_rn(a.x, a.y), b1 = __floats2bfloat162_rn(a.z, a.w);
+                __nv_bfloat162 b2 = __floats2bfloat162_rn(b.x, b.y), b3 = __floats2bfloat162_rn(b.z, b.w);
+                o.x = *reinterpret_cast<unsigned*>(&b0); o.y = *reinterpret_cast<unsigned*>(&b1);
+                o.z = *reinterpret_cast<unsigned*>(&b2); o.w = *reinterpret_cast<unsigned*>(&b3);
+                *reinterpret_cast<uint4*>(dst) = o;
+              } else {
+                const float e[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+                for (int j = 0; j < 8 && sub + j < ncols; ++j) dst[j] = __float2bfloat16_rn(e[j]);
+              }
+            }
+          }
         }
+        __syncwarp();
       }
     }
   }
@@ -235,17 +263,20 @@ template <int BN>
 int launch_grouped(const CUtensorMap& ma, const CUtensorMap& mb, GroupedTcParams p, int max_tiles, cudaStream_t stream) {
   constexpr int STAGE = (GT_M + BN) * GT_K * 2;
   const int nkb = (p.K + GT_K - 1) / GT_K;
-  // a ring that lets two CTAs share an SM (one's epilogue under the other's MMAs)
-  int stages = (100 * 1024) / STAGE;
+  // a ring that lets two CTAs share an SM (one's epilogue under the other's MMAs); DLGO_MOE_TC_RING_KB sets its size
+  static const int ring_kb = [] { const char* e = getenv("DLGO_MOE_TC_RING_KB"); return e ? atoi(e) : 100; }();
+  int stages = (ring_kb * 1024) / STAGE;
+  if (stages > 8) stages = 8;
   if (stages > nkb) stages = nkb;
   if (stages < 2) stages = 2;
   p.stages = stages;
   const int smem = stages * STAGE + 1024 + 256;
-  static int configured = 0;
-  if (configured < smem) {
-    cudaError_t e = cudaFuncSetAttribute(moe_gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
+  if (smem > 227 * 1024) return DLGO_ERR_SIZE;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(moe_gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return (int)e;
-    configured = 110 * 1024;
+    configured = true;
   }
   dim3 grid((p.N + BN - 1) / BN, max_tiles);
   launch_kernel(moe_gemm_tc_kernel<BN>, grid, dim3(GT_THREADS), (size_t)smem, stream, ma, mb, p);
@@ -269,7 +300,8 @@ DLGO_EXPORT int dlgo_moe_gemm_tc(const void* A, long long a_rows, long long lda,
   if (max_tiles <= 0 || max_tiles > 65535 || a_rows <= 0 || experts <= 0) return DLGO_ERR_SIZE;
   if (!dlgo_moe_gemm_tc_takes(N, K)) return DLGO_ERR_SIZE;
   CUtensorMap ma, mb;
-  const int bn = N >= 256 ? 256 : 128;
+  static const int force_bn = [] { const char* e = getenv("DLGO_MOE_TC_BN"); return e ? atoi(e) : 0; }();
+  const int bn = force_bn == 128 || force_bn == 256 ? force_bn : (N >= 256 ? 256 : 128);
   int st = make_map(&ma, A, a_rows, K, lda, GT_M);
   if (st != DLGO_OK) return st;
   st = make_map(&mb, W, (long long)experts * N, K, K, bn);

@@ -122,7 +122,7 @@ class RoutedExperts(FeedForward):
             pairs = T * self.top
             few = pairs <= _FEW_PAIRS_PER_EXPERT * self.num_experts
             hidden = torch.empty((pairs, self.intermediate_size), dtype=x.dtype, device=x.device)
-            pair_out = torch.empty((pairs, d), dtype=torch.float32, device=x.device)
+            pair_out = torch.empty((pairs, d), dtype=x.dtype, device=x.device)    # (sums of these stay fp32)
             if not few and self.on_tensor_cores:
                 # prompts in bfloat16: the tokens' rows copied into sorted order, then both contractions on tcgen05
                 plan = K.moe_plan(idx, self.num_experts, K.MOE_TC_ROWS)
