@@ -32,6 +32,10 @@ _ACTS = {"none": K.ACT_NONE, "relu2": K.ACT_RELU2, "silu": K.ACT_SILU, "gelu_tan
 # pairs per expert (on average) up to which the 8-row tiles run; beyond, the larger tiles
 _FEW_PAIRS_PER_EXPERT = int(os.environ.get("DLGO_MOE_FEW_PAIRS", 8))
 _TENSOR_CORES = os.environ.get("DLGO_MOE_TC", "1") != "0"       # 0: the fp32-pipe tiles also in bfloat16
+# bfloat16: pairs of a step from which the tcgen05 kernel runs instead of the 8-row tiles.  Measured on a B200 at
+# width 2,048 with 56 experts of 1,024, 8 chosen (ms a decode step, 8-row tiles against tcgen05): batch 1, 0.518 /
+# 0.662; batch 2, 0.620 / 0.694; batch 4, 0.745 / 0.717; batch 8, 0.880 / 0.735; batch 32, 1.58 / 0.894.
+_TC_MIN_PAIRS = int(os.environ.get("DLGO_MOE_TC_MIN_PAIRS", 24))
 
 
 class RoutedExperts(FeedForward):
@@ -123,7 +127,7 @@ class RoutedExperts(FeedForward):
             few = pairs <= _FEW_PAIRS_PER_EXPERT * self.num_experts
             hidden = torch.empty((pairs, self.intermediate_size), dtype=x.dtype, device=x.device)
             pair_out = torch.empty((pairs, d), dtype=x.dtype, device=x.device)    # (sums of these stay fp32)
-            if not few and self.on_tensor_cores:
+            if self.on_tensor_cores and pairs >= _TC_MIN_PAIRS:
                 # prompts in bfloat16: the tokens' rows copied into sorted order, then both contractions on tcgen05
                 plan = K.moe_plan(idx, self.num_experts, K.MOE_TC_ROWS)
                 rows = K.moe_gather_rows(plan, x, self.top)
