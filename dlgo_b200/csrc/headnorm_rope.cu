@@ -6,7 +6,8 @@
 // numbers each; `bias` (fp32, one number per column, may be null) is added first.  With `v_from_k` the
 // value of a position is its key as projected (with the bias, before norm and rotation).
 //
-//   head norm (w_q / w_k not null):  u <- u / sqrt(mean(u^2) + eps) * w      (plain weight, per head)
+//   head norm (w_q / w_k not null):  u <- u / sqrt(mean(u^2) + eps) * w      (plain weight, per head; the mean runs
+//   over the first `norm_dim` numbers of a head: a head may be laid out with trailing zeros)
 //   rotation of the first `rot` numbers of a head: (u_i, u_{i + rot/2}) turns by a = pos * freq[i],
 //   with a = float(pos) * freq[i] in fp32 and cos / sin of that fp32 angle.
 //
@@ -31,7 +32,7 @@ headnorm_rope_append_kernel(float* __restrict__ proj, int ld, const float* __res
                             const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
                             const int* __restrict__ page_table, int max_pages, T* __restrict__ kpages,
                             T* __restrict__ vpages, T* __restrict__ q_out, int T_tokens, int Hq, int Hkv, int hd,
-                            int page_size, int v_from_k, int write_cache, int clear) {
+                            int page_size, int v_from_k, int write_cache, int clear, int norm_dim) {
   extern __shared__ float hr_smem[];
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -76,7 +77,7 @@ headnorm_rope_append_kernel(float* __restrict__ proj, int ld, const float* __res
     return;
   }
   ss = warp_sum(ss);
-  const float r = (w != nullptr) ? 1.0f / sqrtf(ss / (float)hd + eps) : 1.0f;
+  const float r = (w != nullptr) ? 1.0f / sqrtf(ss / (float)norm_dim + eps) : 1.0f;
   __syncwarp();
   T* dst = is_q ? q_out + (size_t)t * Hq * hd + (size_t)head * hd : kdst;
   if (dst == nullptr) return;
@@ -101,7 +102,7 @@ template <typename T>
 int launch_headnorm_rope(float* proj, int ld, const float* bias, const float* w_q, const float* w_k, float eps,
                          const float* freq, int rot, const int* token_pos, const int* token_seq, const int* seq_slot,
                          const int* page_table, int max_pages, void* kpages, void* vpages, void* q_out, int T_tokens,
-                         int Hq, int Hkv, int hd, int page_size, int v_from_k, int write_cache, int clear,
+                         int Hq, int Hkv, int hd, int page_size, int v_from_k, int write_cache, int clear, int norm_dim,
                          cudaStream_t stream) {
   const int heads = Hq + Hkv + (v_from_k ? 0 : Hkv);
   const long long items = (long long)T_tokens * heads;
@@ -111,7 +112,7 @@ int launch_headnorm_rope(float* proj, int ld, const float* bias, const float* w_
   if (smem > 48 * 1024) return DLGO_ERR_SIZE;
   launch_kernel(headnorm_rope_append_kernel<T>, dim3((unsigned)blocks), dim3(HR_WARPS * 32), smem, stream, proj, ld,
                 bias, w_q, w_k, eps, freq, rot, token_pos, token_seq, seq_slot, page_table, max_pages, (T*)kpages,
-                (T*)vpages, (T*)q_out, T_tokens, Hq, Hkv, hd, page_size, v_from_k, write_cache, clear);
+                (T*)vpages, (T*)q_out, T_tokens, Hq, Hkv, hd, page_size, v_from_k, write_cache, clear, norm_dim);
   return launch_status();
 }
 
@@ -122,19 +123,20 @@ DLGO_EXPORT int dlgo_headnorm_rope_append(float* proj, int ld, const float* bias
                                           const int* token_seq, const int* seq_slot, const int* page_table,
                                           int max_pages, void* kpages, void* vpages, void* q_out, int dtype, int T,
                                           int Hq, int Hkv, int hd, int page_size, int v_from_k, int write_cache,
-                                          int clear, cudaStream_t stream) {
+                                          int clear, int norm_dim, cudaStream_t stream) {
   if (T <= 0) return DLGO_OK;
   if (Hq <= 0 || Hkv <= 0 || hd <= 0 || rot < 0 || rot > hd || rot % 2) return DLGO_ERR_SIZE;
   if (rot > 0 && freq == nullptr) return DLGO_ERR_SIZE;
+  if (norm_dim <= 0 || norm_dim > hd) return DLGO_ERR_SIZE;
   if (ld < (Hq + Hkv + (v_from_k ? 0 : Hkv)) * hd) return DLGO_ERR_SIZE;
   if (dtype == DLGO_F32)
     return dlgo::launch_headnorm_rope<float>(proj, ld, bias, w_q, w_k, eps, freq, rot, token_pos, token_seq, seq_slot,
                                              page_table, max_pages, kpages, vpages, q_out, T, Hq, Hkv, hd, page_size,
-                                             v_from_k, write_cache, clear, stream);
+                                             v_from_k, write_cache, clear, norm_dim, stream);
   if (dtype == DLGO_BF16)
     return dlgo::launch_headnorm_rope<__nv_bfloat16>(proj, ld, bias, w_q, w_k, eps, freq, rot, token_pos, token_seq,
                                                      seq_slot, page_table, max_pages, kpages, vpages, q_out, T, Hq,
-                                                     Hkv, hd, page_size, v_from_k, write_cache, clear, stream);
+                                                     Hkv, hd, page_size, v_from_k, write_cache, clear, norm_dim, stream);
   return DLGO_ERR_DTYPE;
 }
 

@@ -532,13 +532,14 @@ def headnorm_rope_append(proj: torch.Tensor, bias: Optional[torch.Tensor], w_q: 
                          token_pos: torch.Tensor, token_seq: torch.Tensor, seq_slot: torch.Tensor,
                          page_table: torch.Tensor, kpages: torch.Tensor, vpages: torch.Tensor, num_heads: int,
                          num_kv_heads: int, head_dim: int, values_from_keys: bool, write_cache: bool = True,
-                         clear: bool = False) -> torch.Tensor:
+                         clear: bool = False, norm_dim: Optional[int] = None) -> torch.Tensor:
     """From the fp32 projection ``proj`` [T, ld] (query heads, key heads and, unless ``values_from_keys``, value
     heads; ``bias`` fp32 per column added first): per-head RMS norm of queries and keys with the weights ``w_q`` /
     ``w_k`` (None: no norm), rotation of the first ``rotary_dim`` numbers of each head (pairs (i, i + rotary_dim/2))
     by the fp32 angle ``float(position) * freq[i]``, keys and values stored at their positions' pages (with
     ``values_from_keys`` a value is its key as projected, before norm and rotation).  Returns the queries
-    [T, heads * head_dim] in the cache's type.  ``clear`` leaves zeros in ``proj``."""
+    [T, heads * head_dim] in the cache's type.  ``clear`` leaves zeros in ``proj``.  ``norm_dim``: the number of
+    entries the head norm's mean runs over (heads laid out with trailing zeros; default ``head_dim``)."""
     if proj.dtype != torch.float32 or proj.dim() != 2 or proj.stride(1) != 1:
         raise KernelError("headnorm_rope_append: proj must be 2-D float32 with unit inner stride")
     for n, t in (("bias", bias), ("w_q", w_q), ("w_k", w_k), ("freq", freq)):
@@ -565,7 +566,7 @@ def headnorm_rope_append(proj: torch.Tensor, bias: Optional[torch.Tensor], w_q: 
         _ptr(token_pos), _ptr(token_seq), _ptr(seq_slot), _ptr(page_table), _i(page_table.shape[1]), _ptr(kpages),
         _ptr(vpages), _ptr(q), _i(dtype_code(kpages.dtype)), _i(T), _i(num_heads), _i(num_kv_heads), _i(head_dim),
         _i(kpages.shape[-2]), _i(1 if values_from_keys else 0), _i(1 if write_cache else 0), _i(1 if clear else 0),
-        _stream())
+        _i(norm_dim or head_dim), _stream())
     _check(st, "headnorm_rope_append")
     return q
 

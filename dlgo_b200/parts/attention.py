@@ -257,8 +257,13 @@ class KeysAsValuesAttention(GQAAttention):
                  bias: bool = False, head_norm: bool = False, eps: float = 1e-6, window: Optional[int] = None,
                  position_encoding: Optional[str] = None, cache_group: str = "full",
                  names: Optional[Mapping[str, str]] = None):
-        super().__init__(hidden_size, num_heads, num_kv_heads, head_dim, scale, window, position_encoding, cache_group)
-        self.params.update(bias=bias, head_norm=head_norm, eps=eps, names=names)
+        # A head size that is no multiple of 8 is laid out as the next multiple: the projection gets zero rows, the
+        # output projection zero columns, so the added numbers are zeros everywhere (queries, both cache rows,
+        # attention's result) and change neither a score nor a sum; the head norm's mean runs over the true size.
+        self.true_head_dim = int(head_dim)
+        padded = -(-self.true_head_dim // self.head_multiple) * self.head_multiple
+        super().__init__(hidden_size, num_heads, num_kv_heads, padded, scale, window, position_encoding, cache_group)
+        self.params.update(head_dim=head_dim, bias=bias, head_norm=head_norm, eps=eps, names=names)
         self.bias = bool(bias)
         self.head_norm = bool(head_norm)
         self.eps = float(eps)
@@ -271,26 +276,40 @@ class KeysAsValuesAttention(GQAAttention):
         self.w_knorm: Optional[torch.Tensor] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        n = self.names
-        specs = {n["q"]: ParamSpec((self.q_dim, self.hidden_size)), n["k"]: ParamSpec((self.kv_dim, self.hidden_size)),
-                 n["out"]: ParamSpec((self.hidden_size, self.q_dim))}
+        n, hd = self.names, self.true_head_dim
+        q_dim, kv_dim = self.num_heads * hd, self.num_kv_heads * hd
+        specs = {n["q"]: ParamSpec((q_dim, self.hidden_size)), n["k"]: ParamSpec((kv_dim, self.hidden_size)),
+                 n["out"]: ParamSpec((self.hidden_size, q_dim))}
         if self.bias:
-            specs[n["q_bias"]] = ParamSpec((self.q_dim,))
-            specs[n["k_bias"]] = ParamSpec((self.kv_dim,))
+            specs[n["q_bias"]] = ParamSpec((q_dim,))
+            specs[n["k_bias"]] = ParamSpec((kv_dim,))
         if self.head_norm:
-            specs[n["q_norm"]] = ParamSpec((self.head_dim,), "one_plus_normal")
-            specs[n["k_norm"]] = ParamSpec((self.head_dim,), "one_plus_normal")
+            specs[n["q_norm"]] = ParamSpec((hd,), "one_plus_normal")
+            specs[n["k_norm"]] = ParamSpec((hd,), "one_plus_normal")
         return specs
+
+    def _pad_heads(self, t: torch.Tensor, dim: int) -> torch.Tensor:
+        """``t`` with every head's ``true_head_dim`` entries along ``dim`` followed by zeros up to ``head_dim``."""
+        hd, hp = self.true_head_dim, self.head_dim
+        if hd == hp:
+            return t
+        shape = list(t.shape)
+        heads = shape[dim] // hd
+        t = t.reshape(shape[:dim] + [heads, hd] + shape[dim + 1:])
+        pad = torch.zeros(shape[:dim] + [heads, hp - hd] + shape[dim + 1:], dtype=t.dtype, device=t.device)
+        return torch.cat([t, pad], dim=dim + 1).reshape(shape[:dim] + [heads * hp] + shape[dim + 1:])
 
     def load(self, get: Callable[[str], torch.Tensor], runtime: Any) -> None:
         n = self.names
-        self.wqk = Linear(torch.cat([runtime.compute_copy(get(n["q"])), runtime.compute_copy(get(n["k"]))], dim=0), runtime)
-        self.wo = Linear(get(n["out"]), runtime)
+        self.wqk = Linear(torch.cat([self._pad_heads(runtime.compute_copy(get(n["q"])), 0),
+                                     self._pad_heads(runtime.compute_copy(get(n["k"])), 0)], dim=0), runtime)
+        self.wo = Linear(self._pad_heads(runtime.compute_copy(get(n["out"])), 1).contiguous(), runtime)
         if self.bias:       # added to the fp32 result of the projection
-            self.b_qk = torch.cat([get(n["q_bias"]).to(torch.float32), get(n["k_bias"]).to(torch.float32)]).contiguous()
+            self.b_qk = torch.cat([self._pad_heads(get(n["q_bias"]).to(torch.float32), 0),
+                                   self._pad_heads(get(n["k_bias"]).to(torch.float32), 0)]).contiguous()
         if self.head_norm:  # norms are 32-bit in every precision
-            self.w_qnorm = get(n["q_norm"]).to(torch.float32).contiguous()
-            self.w_knorm = get(n["k_norm"]).to(torch.float32).contiguous()
+            self.w_qnorm = self._pad_heads(get(n["q_norm"]).to(torch.float32), 0).contiguous()
+            self.w_knorm = self._pad_heads(get(n["k_norm"]).to(torch.float32), 0).contiguous()
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: Any, cache: Any,
                 state: Optional[torch.Tensor], positions: Mapping[str, PositionEncoding]) -> None:
@@ -313,7 +332,8 @@ class KeysAsValuesAttention(GQAAttention):
             clear = False
         q = K.headnorm_rope_append(proj, self.b_qk, self.w_qnorm, self.w_knorm, self.eps, freq, rot, ctx.token_pos,
                                    ctx.token_seq, ctx.seq_slot, cache.page_table, cache.keys, cache.values,
-                                   self.num_heads, self.num_kv_heads, self.head_dim, True, cache.writes, clear)
+                                   self.num_heads, self.num_kv_heads, self.head_dim, True, cache.writes, clear,
+                                   norm_dim=self.true_head_dim)
         out = torch.empty((T, self.q_dim), dtype=act, device=x.device)
         self._attend(q, ctx, cache, out, decode_kernel, mma, n_splits, scratch, counters, pages)
         self._project_out(out, residual, ctx)

@@ -40,6 +40,17 @@ def test_run_order_shares_tensors_but_not_caches():
     assert [(n.num_kv_heads, n.head_dim, n.planes, n.window) for n in needs] == [(3, 24, 2, None)] * 2 + [(1, 32, 2, None), (3, 24, 2, None)]
 
 
+def test_a_head_size_that_is_no_multiple_of_eight_is_laid_out_as_the_next_one():
+    cfg = {"architecture": "Monolix", "vocab": 50, "width": 40, "norm": {"eps": 1e-6}, "postln_alpha": 1.0,
+           "layers": [layer(att(3, 1, 20, 10), None)]}
+    model = CausalLM(config_from_dict(cfg).architecture_spec())
+    shape = {n: tuple(ps.shape) for n, ps in model.expected_tensors().items()}
+    assert shape["l0.mix.q"] == (60, 40) and shape["l0.mix.k"] == (20, 40) and shape["l0.mix.o"] == (40, 60)
+    assert shape["l0.mix.q.norm"] == (20,)
+    needs, _, _ = model.cache_needs()
+    assert (needs[0].num_kv_heads, needs[0].head_dim) == (1, 24)
+
+
 def test_expected_tensors():
     t = CausalLM(config_from_dict(CONFIGS["P"]).architecture_spec()).expected_tensors()
     shape = {n: tuple(ps.shape) for n, ps in t.items()}

@@ -311,6 +311,25 @@ def test_rotation_turns_with_the_distance(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("dim, rot", [(20, 10), (12, 12), (36, 0), (100, 50)])
+def test_head_sizes_that_are_no_multiple_of_eight(dim, rot, dtype):
+    """Such a head is laid out with trailing zeros; norm, rotation, scores and sums see the true size."""
+    cfg = {"architecture": "Monolix", "vocab": 90, "width": 56, "norm": {"eps": 1e-6}, "postln_alpha": 1.5,
+           "layers": [layer(att(4, 2, dim, rot, base=300.0, scale=0.4), moe(24, 3, 1, 2, 2, 1, 16)),
+                      layer(att(4, 2, dim, rot, base=300.0, scale=0.4), moe(24, 3, 1, 2, 2, 1, 16), 0)]}
+    w = make_weights(cfg, dim, mild=(dtype == "bfloat16"))
+    tokens = random_tokens(150, cfg["vocab"], 6)
+    ref = plain_of(cfg, w, tokens)
+    eng = engine_of(cfg, w, dtype)
+    assert_rows(run_whole(eng, tokens), ref, dtype, "whole")
+    s = eng.take_slot()
+    got = [eng.step([s], [tokens[:70]], [list(range(70))]).clone()]
+    got += [eng.step([s], [tokens[p:p + 1]]).clone() for p in range(70, 150)]
+    eng.free_slot(s)
+    assert_rows(torch.cat(got), ref, dtype, "prefill then decode")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_values_are_the_keys_as_projected(dtype):
     """What is summed is the key before norm and rotation, with its bias: an oracle that sums the normed and
     rotated key instead differs visibly, and the engine agrees with the right one."""
