@@ -260,11 +260,18 @@ int make_map(CUtensorMap* m, const void* base, long long rows, int K, long long 
 }
 
 template <int BN>
-int launch_grouped(const CUtensorMap& ma, const CUtensorMap& mb, GroupedTcParams p, int max_tiles, cudaStream_t stream) {
+int launch_grouped(const CUtensorMap& ma, const CUtensorMap& mb, GroupedTcParams p, int max_tiles, int ring_default_kb,
+                   cudaStream_t stream) {
   constexpr int STAGE = (GT_M + BN) * GT_K * 2;
   const int nkb = (p.K + GT_K - 1) / GT_K;
-  // a ring that lets two CTAs share an SM (one's epilogue under the other's MMAs); DLGO_MOE_TC_RING_KB sets its size
-  static const int ring_kb = [] { const char* e = getenv("DLGO_MOE_TC_RING_KB"); return e ? atoi(e) : 100; }();
+  // a small ring, so that several CTAs share an SM (one's epilogue and start-up under the others' MMAs): measured on a
+  // B200 (width 2,048, 56 experts of 1,024, 8 chosen; prompt of 2,048 tokens / decode step at batch 8, ms): tiles 256
+  // wide with 100 KB 3.29 / 0.734, with 150 KB 3.91 / 0.801; 128 wide with 100 KB 3.32 / 0.668, with 66 KB (two
+  // stages, three CTAs an SM) 3.16 / 0.629; 64 wide with 75 KB (three stages, three CTAs an SM) 3.29 / 0.597.  So
+  // prompts take 128 x 128 tiles and steps of few rows 128 x 64.  DLGO_MOE_TC_RING_KB and DLGO_MOE_TC_BN (64, 128,
+  // 256) override.
+  static const int ring_env = [] { const char* e = getenv("DLGO_MOE_TC_RING_KB"); return e ? atoi(e) : 0; }();
+  const int ring_kb = ring_env > 0 ? ring_env : ring_default_kb;
   int stages = (ring_kb * 1024) / STAGE;
   if (stages > 8) stages = 8;
   if (stages > nkb) stages = nkb;
@@ -301,13 +308,15 @@ DLGO_EXPORT int dlgo_moe_gemm_tc(const void* A, long long a_rows, long long lda,
   if (!dlgo_moe_gemm_tc_takes(N, K)) return DLGO_ERR_SIZE;
   CUtensorMap ma, mb;
   static const int force_bn = [] { const char* e = getenv("DLGO_MOE_TC_BN"); return e ? atoi(e) : 0; }();
-  const int bn = force_bn == 128 || force_bn == 256 ? force_bn : (N >= 256 ? 256 : 128);
+  const int bn = force_bn == 64 || force_bn == 128 || force_bn == 256 ? force_bn : (a_rows <= 2048 ? 64 : 128);
   int st = make_map(&ma, A, a_rows, K, lda, GT_M);
   if (st != DLGO_OK) return st;
   st = make_map(&mb, W, (long long)experts * N, K, K, bn);
   if (st != DLGO_OK) return st;
   GroupedTcParams p{offsets, tile_expert, tile_row0, n_tiles, o_scatter, out, ldo, out_f32, act, N, K, 0};
-  return bn == 256 ? launch_grouped<256>(ma, mb, p, max_tiles, stream) : launch_grouped<128>(ma, mb, p, max_tiles, stream);
+  if (bn == 256) return launch_grouped<256>(ma, mb, p, max_tiles, 100, stream);
+  if (bn == 64) return launch_grouped<64>(ma, mb, p, max_tiles, 75, stream);
+  return launch_grouped<128>(ma, mb, p, max_tiles, 66, stream);
 }
 
 // dst[r][:] = src[sorted_pair[r] / div][:] for the rows that belong to an expert; rows of `row_bytes` (a multiple of 16)

@@ -35,7 +35,8 @@ _TENSOR_CORES = os.environ.get("DLGO_MOE_TC", "1") != "0"       # 0: the fp32-pi
 # bfloat16: pairs of a step from which the tcgen05 kernel runs instead of the 8-row tiles.  Measured on a B200 at
 # width 2,048 with 56 experts of 1,024, 8 chosen (ms a decode step, 8-row tiles against tcgen05): batch 1, 0.518 /
 # 0.662; batch 2, 0.620 / 0.694; batch 4, 0.745 / 0.717; batch 8, 0.880 / 0.735; batch 32, 1.58 / 0.894.
-_TC_MIN_PAIRS = int(os.environ.get("DLGO_MOE_TC_MIN_PAIRS", 24))
+# With experts of a megabyte (width 1,024, experts of 512) the 8-row tiles still win at 32 pairs: 0.372 / 0.420.
+_TC_MIN_PAIRS = int(os.environ.get("DLGO_MOE_TC_MIN_PAIRS", 0))      # 0: 24, or 128 for experts below 2 MB
 
 
 class RoutedExperts(FeedForward):
@@ -127,7 +128,8 @@ class RoutedExperts(FeedForward):
             few = pairs <= _FEW_PAIRS_PER_EXPERT * self.num_experts
             hidden = torch.empty((pairs, self.intermediate_size), dtype=x.dtype, device=x.device)
             pair_out = torch.empty((pairs, d), dtype=x.dtype, device=x.device)    # (sums of these stay fp32)
-            if self.on_tensor_cores and pairs >= _TC_MIN_PAIRS:
+            tc_from = _TC_MIN_PAIRS or (24 if self.intermediate_size * self.hidden_size >= (1 << 20) else 128)
+            if self.on_tensor_cores and pairs >= tc_from:
                 # prompts in bfloat16: the tokens' rows copied into sorted order, then both contractions on tcgen05
                 plan = K.moe_plan(idx, self.num_experts, K.MOE_TC_ROWS)
                 rows = K.moe_gather_rows(plan, x, self.top)
