@@ -2,7 +2,6 @@
 whole models through the engine's step function, its cache, and the public entry point."""
 import copy
 import json
-import math
 import os
 
 import pytest
@@ -65,7 +64,7 @@ def test_norm_after_the_sum(T, act_dtype):
     for d in (40, 72, 1000):
         x, y = torch.randn(T, d, generator=g), torch.randn(T, d, generator=g)
         ls, w = 1 + 0.3 * torch.randn(d, generator=g), 1 + 0.2 * torch.randn(d, generator=g)
-        skip, eps = 2.5, 1e-5
+        skip, eps = 1.75, 1e-5
         u = skip * x.double() + ls.double() * y.double()
         ref = P.rms(u, eps) * w.double()
         xd, yd = x.to(DEV), y.to(DEV)
@@ -79,13 +78,13 @@ def test_norm_after_the_sum(T, act_dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("Hq, Hkv, hd, rot", [(6, 3, 24, 12), (4, 4, 16, 16), (5, 1, 40, 8), (2, 2, 64, 0), (8, 2, 128, 64)])
+@pytest.mark.parametrize("Hq, Hkv, hd, rot", [(6, 3, 24, 12), (4, 4, 16, 16), (5, 1, 40, 8), (2, 2, 64, 0), (8, 4, 128, 64)])
 def test_head_norm_rotation_and_append(Hq, Hkv, hd, rot, dtype):
     """Bias, per-head norm, rotation at far positions, and the cache rows: the key row normed and rotated, the
     value row the key as projected."""
     from dlgo_b200.csrc import kernels as K
     g = torch.Generator().manual_seed(hd)
-    T, ps, base, eps = 7, 64, 250000.0, 1e-6
+    T, ps, base, eps = 7, 64, 30000.0, 1e-6
     pos = torch.tensor([0, 1, 63, 64, 1000, 70001, 5], dtype=torch.int32)
     cols = (Hq + Hkv) * hd
     proj = torch.randn(T, cols, generator=g)
@@ -135,7 +134,7 @@ def test_head_norm_rotation_and_append(Hq, Hkv, hd, rot, dtype):
 
 def _route_cases():
     # (outputs, experts with tensors, top, groups, keep)
-    return [(16, 12, 4, 4, 3), (8, 6, 3, 4, 2), (5, 5, 1, 1, 1), (4, 1, 2, 2, 2), (8, 8, 2, 2, 1), (64, 60, 8, 8, 4),
+    return [(20, 15, 4, 5, 3), (8, 6, 3, 4, 2), (5, 5, 1, 1, 1), (4, 1, 2, 2, 2), (8, 8, 2, 2, 1), (64, 60, 8, 8, 4),
             (33, 30, 5, 3, 2)]
 
 
@@ -165,7 +164,7 @@ def test_router_choice_and_weights(n, E, top, groups, keep):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("T", [1, 5, 33, 300])
-@pytest.mark.parametrize("d, ff, E, ident, top", [(48, 40, 6, 2, 3), (72, 24, 1, 3, 2), (50, 36, 5, 0, 1), (128, 96, 12, 4, 4)])
+@pytest.mark.parametrize("d, ff, E, ident, top", [(48, 40, 6, 2, 3), (72, 24, 1, 3, 2), (50, 36, 5, 0, 1), (128, 88, 10, 3, 4)])
 def test_experts_grouped_contractions(T, d, ff, E, ident, top, dtype):
     """Plan, the two grouped contractions (tiles of 8 rows and of 64) and the combine against a loop over
     tokens; identity experts return the input; sizes that are no multiple of 8 take the scalar loads."""
@@ -201,7 +200,7 @@ def test_experts_grouped_contractions(T, d, ff, E, ident, top, dtype):
 
 
 @pytest.mark.parametrize("T", [3, 130, 700])
-@pytest.mark.parametrize("d, ff, E, ident, top", [(256, 192, 5, 1, 3), (128, 96, 12, 4, 4), (72, 40, 3, 0, 2), (512, 320, 2, 0, 1)])
+@pytest.mark.parametrize("d, ff, E, ident, top", [(256, 192, 5, 1, 3), (128, 80, 11, 3, 4), (72, 40, 3, 0, 2), (512, 320, 2, 0, 1)])
 def test_experts_on_the_tensor_cores(T, d, ff, E, ident, top):
     """The grouped contraction on tcgen05 (tiles of 128 sorted rows; an expert's last tile runs into the next
     expert's rows, a weight tile into the next expert's weight: neither may be stored) against the fp32-pipe
