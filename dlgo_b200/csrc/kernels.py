@@ -602,9 +602,11 @@ MOE_FEW_ROWS, MOE_TILE_ROWS, MOE_TC_ROWS = 8, 64, 128      # rows per tile of th
 
 def moe_router(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], n_outputs: int,
                has_gate: bool, top: int, groups: int, keep: int, sigmoid_scores: bool = False,
-               renormalize: bool = False):
+               renormalize: bool = False, plan: Optional[tuple] = None):
     """Router of a mixture of experts for ``h`` [T, d]: returns (chosen outputs [T, top] int32, their weights
-    [T, top] fp32, gate [T] fp32 or None).  ``w_router`` is fp32 [n_outputs (+ 1 gate row), d]."""
+    [T, top] fp32, gate [T] fp32 or None, plan).  ``w_router`` is fp32 [n_outputs (+ 1 gate row), d].
+    ``plan`` = (experts that hold tensors, rows per tile): the :class:`MoEPlan` of :func:`moe_plan` is made as well,
+    in the choice's own launch where the step has few tokens, else by a launch of its own; without it None."""
     _need(w_router, torch.float32, "w_router")
     if h.dim() != 2 or h.stride(1) != 1:
         raise KernelError("moe_router: h must be 2-D with unit inner stride")
@@ -620,12 +622,20 @@ def moe_router(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[tor
     wt = torch.empty((T, top), dtype=torch.float32, device=h.device)
     gate = torch.empty((T,), dtype=torch.float32, device=h.device) if has_gate else None
     z = torch.empty((T, rows), dtype=torch.float32, device=h.device)
+    p = _empty_plan(T * top, plan[0], plan[1], h.device) if plan is not None and plan[0] > 0 else None
+    fused = ctypes.c_int(0)
     st = _lib("moe").dlgo_moe_router(
         _ptr(h), _i(dtype_code(h.dtype)), _i(h.stride(0)), _ptr(w_router), _ptr(correction), _ptr(z), _ptr(idx),
         _ptr(wt), _ptr(gate), _i(T), _i(d), _i(n_outputs), _i(1 if has_gate else 0), _i(top), _i(groups), _i(keep),
-        _i(1 if sigmoid_scores else 0), _i(1 if renormalize else 0), _stream())
+        _i(1 if sigmoid_scores else 0), _i(1 if renormalize else 0), _i(plan[0] if p is not None else 0),
+        _i(plan[1] if p is not None else 0), _ptr(p.offsets if p is not None else None),
+        _ptr(p.sorted_pair if p is not None else None), _ptr(p.tile_expert if p is not None else None),
+        _ptr(p.tile_row0 if p is not None else None), _ptr(p.n_tiles if p is not None else None),
+        _i(p.max_tiles if p is not None else 0), ctypes.byref(fused), _stream())
     _check(st, "moe_router", 2)
-    return idx, wt, gate
+    if p is not None and not fused.value:
+        p = moe_plan(idx, plan[0], plan[1], p)
+    return idx, wt, gate, p
 
 
 class MoEPlan:
@@ -634,21 +644,26 @@ class MoEPlan:
     __slots__ = ("offsets", "sorted_pair", "tile_expert", "tile_row0", "n_tiles", "max_tiles", "tile_rows", "pairs")
 
 
-def moe_plan(idx: torch.Tensor, n_experts: int, tile_rows: int) -> MoEPlan:
-    """Sort the pairs of ``idx`` [T, top] by expert, on the device: offsets per expert, the sorted list of pair
-    numbers (token * top + choice), and row tiles of ``tile_rows`` rows.  Outputs >= ``n_experts`` enter no list."""
-    _need(idx, torch.int32, "idx")
-    pairs = idx.numel()
+def _empty_plan(pairs: int, n_experts: int, tile_rows: int, device: torch.device) -> MoEPlan:
     p = MoEPlan()
     p.pairs, p.tile_rows = pairs, tile_rows
     p.max_tiles = (pairs + tile_rows - 1) // tile_rows + n_experts
-    buf = torch.empty((n_experts + 1 + pairs + 2 * p.max_tiles + 1,), dtype=torch.int32, device=idx.device)
+    buf = torch.empty((n_experts + 1 + pairs + 2 * p.max_tiles + 1,), dtype=torch.int32, device=device)
     o = 0
     p.offsets = buf[o:o + n_experts + 1]; o += n_experts + 1
     p.sorted_pair = buf[o:o + pairs]; o += pairs
     p.tile_expert = buf[o:o + p.max_tiles]; o += p.max_tiles
     p.tile_row0 = buf[o:o + p.max_tiles]; o += p.max_tiles
     p.n_tiles = buf[o:o + 1]
+    return p
+
+
+def moe_plan(idx: torch.Tensor, n_experts: int, tile_rows: int, into: Optional[MoEPlan] = None) -> MoEPlan:
+    """Sort the pairs of ``idx`` [T, top] by expert, on the device: offsets per expert, the sorted list of pair
+    numbers (token * top + choice), and row tiles of ``tile_rows`` rows.  Outputs >= ``n_experts`` enter no list."""
+    _need(idx, torch.int32, "idx")
+    pairs = idx.numel()
+    p = into if into is not None else _empty_plan(pairs, n_experts, tile_rows, idx.device)
     st = _lib("moe").dlgo_moe_plan(_ptr(idx), _i(pairs), _i(n_experts), _i(tile_rows), _ptr(p.offsets),
                                    _ptr(p.sorted_pair), _ptr(p.tile_expert), _ptr(p.tile_row0), _ptr(p.n_tiles),
                                    _i(p.max_tiles), _stream())

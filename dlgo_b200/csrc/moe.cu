@@ -145,20 +145,13 @@ moe_logits_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ Wr
 // The choice: a warp per token over its row of logits.
 constexpr int RC_WARPS = 4;
 
-__global__ void __launch_bounds__(RC_WARPS * 32)
-moe_choose_kernel(const float* __restrict__ zg, const float* __restrict__ corr, int* __restrict__ idx,
-                  float* __restrict__ wt, float* __restrict__ gate, int tokens, int n, int has_gate, int top, int groups,
-                  int keep, int sigmoid_scores, int renormalize) {
-  extern __shared__ float rt_smem[];
-  pdl_launch_dependents();
+// One token's choice by one warp; zt / ct / gt are the warp's scratch rows (rows, n and groups floats).
+__device__ __forceinline__ void choose_token(const float* __restrict__ zg, const float* __restrict__ corr,
+                                             int* __restrict__ idx, float* __restrict__ wt, float* __restrict__ gate,
+                                             int t, int n, int has_gate, int top, int groups, int keep,
+                                             int sigmoid_scores, int renormalize, float* zt, float* ct, float* gt,
+                                             int lane) {
   const int rows = n + (has_gate ? 1 : 0);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  float* zt = rt_smem + (size_t)warp * (rows + n + groups);      // scores
-  float* ct = zt + rows;                                          // choice scores
-  float* gt = ct + n;                                             // group scores
-  const int t = blockIdx.x * RC_WARPS + warp;
-  pdl_wait();
-  if (t >= tokens) return;
   for (int j = lane; j < rows; j += 32) zt[j] = zg[(size_t)t * rows + j];
   __syncwarp();
   if (has_gate && lane == 0) gate[t] = 1.f / (1.f + expf(-zt[n]));
@@ -223,20 +216,30 @@ moe_choose_kernel(const float* __restrict__ zg, const float* __restrict__ corr, 
     for (int r = lane; r < top; r += 32) wt[(size_t)t * top + r] /= wsum;
 }
 
+__global__ void __launch_bounds__(RC_WARPS * 32)
+moe_choose_kernel(const float* __restrict__ zg, const float* __restrict__ corr, int* __restrict__ idx,
+                  float* __restrict__ wt, float* __restrict__ gate, int tokens, int n, int has_gate, int top, int groups,
+                  int keep, int sigmoid_scores, int renormalize) {
+  extern __shared__ float rt_smem[];
+  pdl_launch_dependents();
+  const int rows = n + (has_gate ? 1 : 0);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float* zt = rt_smem + (size_t)warp * (rows + n + groups);      // scores
+  const int t = blockIdx.x * RC_WARPS + warp;
+  pdl_wait();
+  if (t >= tokens) return;
+  choose_token(zg, corr, idx, wt, gate, t, n, has_gate, top, groups, keep, sigmoid_scores, renormalize, zt, zt + rows,
+               zt + rows + n, lane);
+}
+
 // -------------------------------------------------------------------------------------------- plan
 constexpr int PLAN_THREADS = 1024;
 
-__global__ void __launch_bounds__(PLAN_THREADS)
-moe_plan_kernel(const int* __restrict__ idx, int pairs, int n_experts, int tile_rows, int* __restrict__ offsets,
-                int* __restrict__ sorted_pair, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
-                int* __restrict__ n_tiles, int max_tiles) {
-  extern __shared__ int pl_smem[];
-  int* count = pl_smem;                  // [n_experts]
-  int* cursor = count + n_experts;       // [n_experts]
-  pdl_launch_dependents();
-  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) count[e] = 0;
-  __syncthreads();
-  pdl_wait();
+// The whole block; count / cursor are n_experts ints of shared memory each, count zeroed (and a barrier passed).
+__device__ __forceinline__ void plan_block(const int* __restrict__ idx, int pairs, int n_experts, int tile_rows,
+                                           int* __restrict__ offsets, int* __restrict__ sorted_pair,
+                                           int* __restrict__ tile_expert, int* __restrict__ tile_row0,
+                                           int* __restrict__ n_tiles, int max_tiles, int* count, int* cursor) {
   for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
     const int e = idx[i];
     if (e >= 0 && e < n_experts) atomicAdd(&count[e], 1);
@@ -264,6 +267,47 @@ moe_plan_kernel(const int* __restrict__ idx, int pairs, int n_experts, int tile_
     const int e = idx[i];
     if (e >= 0 && e < n_experts) sorted_pair[atomicAdd(&cursor[e], 1)] = i;
   }
+}
+
+__global__ void __launch_bounds__(PLAN_THREADS)
+moe_plan_kernel(const int* __restrict__ idx, int pairs, int n_experts, int tile_rows, int* __restrict__ offsets,
+                int* __restrict__ sorted_pair, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
+                int* __restrict__ n_tiles, int max_tiles) {
+  extern __shared__ int pl_smem[];
+  int* count = pl_smem;                  // [n_experts]
+  int* cursor = count + n_experts;       // [n_experts]
+  pdl_launch_dependents();
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) count[e] = 0;
+  __syncthreads();
+  pdl_wait();
+  plan_block(idx, pairs, n_experts, tile_rows, offsets, sorted_pair, tile_expert, tile_row0, n_tiles, max_tiles, count,
+             cursor);
+}
+
+// Choice and plan of a step of few tokens in one launch: one block, a warp per token in turn, then the plan.
+__global__ void __launch_bounds__(PLAN_THREADS)
+moe_choose_plan_kernel(const float* __restrict__ zg, const float* __restrict__ corr, int* __restrict__ idx,
+                       float* __restrict__ wt, float* __restrict__ gate, int tokens, int n, int has_gate, int top,
+                       int groups, int keep, int sigmoid_scores, int renormalize, int n_experts, int tile_rows,
+                       int* __restrict__ offsets, int* __restrict__ sorted_pair, int* __restrict__ tile_expert,
+                       int* __restrict__ tile_row0, int* __restrict__ n_tiles, int max_tiles) {
+  extern __shared__ float rt_smem[];
+  pdl_launch_dependents();
+  const int rows = n + (has_gate ? 1 : 0);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  float* zt = rt_smem + (size_t)warp * (rows + n + groups);
+  int* count = reinterpret_cast<int*>(rt_smem + (size_t)n_warps * (rows + n + groups));
+  int* cursor = count + n_experts;
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) count[e] = 0;
+  pdl_wait();
+  for (int t = warp; t < tokens; t += n_warps) {
+    choose_token(zg, corr, idx, wt, gate, t, n, has_gate, top, groups, keep, sigmoid_scores, renormalize, zt, zt + rows,
+                 zt + rows + n, lane);
+    __syncwarp();
+  }
+  __syncthreads();          // every choice is written (and the counts are zero) before anyone counts
+  plan_block(idx, tokens * top, n_experts, tile_rows, offsets, sorted_pair, tile_expert, tile_row0, n_tiles, max_tiles,
+             count, cursor);
 }
 
 // ------------------------------------------------------------------ grouped contraction: few rows
@@ -530,10 +574,14 @@ static void launch_logits(const void* h, int ldh, const float* Wr, float* z, int
   }
 }
 
-// Two launches: the logits z [tokens, n (+ 1)] (scratch, fp32), then the choice.
+// Two launches: the logits z [tokens, n (+ 1)] (scratch, fp32), then the choice.  With plan_experts > 0 and few
+// tokens the second launch also makes the plan (as dlgo_moe_plan would from idx); *fused says whether it did.
 DLGO_EXPORT int dlgo_moe_router(const void* h, int dtype, int ldh, const float* Wr, const float* corr, float* z, int* idx,
                                 float* wt, float* gate, int tokens, int d, int n, int has_gate, int top, int groups,
-                                int keep, int sigmoid_scores, int renormalize, cudaStream_t stream) {
+                                int keep, int sigmoid_scores, int renormalize, int plan_experts, int tile_rows,
+                                int* offsets, int* sorted_pair, int* tile_expert, int* tile_row0, int* n_tiles,
+                                int max_tiles, int* fused, cudaStream_t stream) {
+  if (fused != nullptr) *fused = 0;
   if (tokens <= 0) return DLGO_OK;
   if (n <= 0 || top <= 0 || top > n || groups <= 0 || n % groups || keep <= 0 || keep > groups || d <= 0)
     return DLGO_ERR_SIZE;
@@ -545,6 +593,18 @@ DLGO_EXPORT int dlgo_moe_router(const void* h, int dtype, int ldh, const float* 
   else return DLGO_ERR_DTYPE;
   int st = launch_status();
   if (st != DLGO_OK) return st;
+  if (plan_experts > 0 && fused != nullptr && tokens <= 64) {
+    const int warps = tokens <= 8 ? 8 : (tokens <= 16 ? 16 : 32);
+    const size_t both = sizeof(float) * warps * ((size_t)rows + n + groups) + sizeof(int) * 2 * (size_t)plan_experts;
+    const int pairs = tokens * top;
+    if (both <= 48 * 1024 && tile_rows > 0 && max_tiles >= (pairs + tile_rows - 1) / tile_rows + plan_experts) {
+      launch_kernel(moe_choose_plan_kernel, dim3(1), dim3(warps * 32), both, stream, (const float*)z, corr, idx, wt, gate,
+                    tokens, n, has_gate, top, groups, keep, sigmoid_scores, renormalize, plan_experts, tile_rows, offsets,
+                    sorted_pair, tile_expert, tile_row0, n_tiles, max_tiles);
+      *fused = 1;
+      return launch_status();
+    }
+  }
   launch_kernel(moe_choose_kernel, dim3((tokens + RC_WARPS - 1) / RC_WARPS), dim3(RC_WARPS * 32), smem, stream,
                 (const float*)z, corr, idx, wt, gate, tokens, n, has_gate, top, groups, keep, sigmoid_scores, renormalize);
   return launch_status();

@@ -121,23 +121,25 @@ class RoutedExperts(FeedForward):
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: Any) -> None:
         T, d = x.shape
-        idx, wt, gate = K.moe_router(x, self.w_router, self.b_choice, self.n_outputs, self.shared_gate, self.top,
-                                     self.group_count, self.group_keep, self.sigmoid_scores, self.renormalize)
+        pairs = T * self.top
+        # which grouped kernel the step takes decides the plan's tile rows; the plan is made with the choice
+        tc_from = _TC_MIN_PAIRS or (24 if self.intermediate_size * self.hidden_size >= (1 << 20) else 128)
+        on_tc = self.on_tensor_cores and pairs >= tc_from
+        few = pairs <= _FEW_PAIRS_PER_EXPERT * max(self.num_experts, 1)
+        tile_rows = K.MOE_TC_ROWS if on_tc else (K.MOE_FEW_ROWS if few else K.MOE_TILE_ROWS)
+        idx, wt, gate, plan = K.moe_router(x, self.w_router, self.b_choice, self.n_outputs, self.shared_gate, self.top,
+                                           self.group_count, self.group_keep, self.sigmoid_scores, self.renormalize,
+                                           plan=(self.num_experts, tile_rows))
         pair_out = None
         if self.num_experts:
-            pairs = T * self.top
-            few = pairs <= _FEW_PAIRS_PER_EXPERT * self.num_experts
             hidden = torch.empty((pairs, self.intermediate_size), dtype=x.dtype, device=x.device)
             pair_out = torch.empty((pairs, d), dtype=x.dtype, device=x.device)    # (sums of these stay fp32)
-            tc_from = _TC_MIN_PAIRS or (24 if self.intermediate_size * self.hidden_size >= (1 << 20) else 128)
-            if self.on_tensor_cores and pairs >= tc_from:
-                # prompts in bfloat16: the tokens' rows copied into sorted order, then both contractions on tcgen05
-                plan = K.moe_plan(idx, self.num_experts, K.MOE_TC_ROWS)
+            if on_tc:
+                # bfloat16: the tokens' rows copied into sorted order, then both contractions on tcgen05
                 rows = K.moe_gather_rows(plan, x, self.top)
                 K.moe_gemm_tc(plan, rows, self.w_up, hidden, False, self.act)
                 K.moe_gemm_tc(plan, hidden, self.w_down, pair_out, True, K.ACT_NONE)
             else:
-                plan = K.moe_plan(idx, self.num_experts, K.MOE_FEW_ROWS if few else K.MOE_TILE_ROWS)
                 K.moe_gemm(plan, x, self.w_up, hidden, self.top, False, self.act)          # rows gathered by token
                 K.moe_gemm(plan, hidden, self.w_down, pair_out, None, True, K.ACT_NONE)    # rows scattered by pair
         shared = None

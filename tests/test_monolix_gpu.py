@@ -149,15 +149,28 @@ def test_router_choice_and_weights(n, E, top, groups, keep):
     Wr = 2.0 * torch.randn(n, d, generator=g) / d ** 0.5
     wg = torch.randn(1, d, generator=g) / d ** 0.5
     corr = 0.3 * torch.randn(n, generator=g) - 0.2                # mostly negative choice scores
-    idx, wt, gate = K.moe_router(h.to(DEV), torch.cat([Wr, wg]).to(DEV), corr.to(DEV), n, True, top, groups, keep)
+    idx, wt, gate, plan = K.moe_router(h.to(DEV), torch.cat([Wr, wg]).to(DEV), corr.to(DEV), n, True, top, groups, keep,
+                                       plan=(E, K.MOE_FEW_ROWS))
     z = h.double() @ Wr.double().T
     for t in range(T):
         want_idx, want_w = P.route(z[t], corr.double(), top, groups, keep)
         assert idx[t].tolist() == want_idx, (t, idx[t].tolist(), want_idx)
         assert torch.allclose(wt[t].cpu().double(), want_w, rtol=1e-5, atol=1e-7)
     assert torch.allclose(gate.cpu().double(), torch.sigmoid(h.double() @ wg.double().T)[:, 0], rtol=1e-5, atol=1e-7)
+    # the plan made along with the choice (in the same launch for the first tokens alone) equals one made from idx
+    for toks in (T, 5):
+        i2, _, _, p2 = K.moe_router(h[:toks].to(DEV), torch.cat([Wr, wg]).to(DEV), corr.to(DEV), n, True, top, groups,
+                                    keep, plan=(E, K.MOE_FEW_ROWS))
+        want = K.moe_plan(i2, E, K.MOE_FEW_ROWS)
+        assert torch.equal(i2, idx[:toks]) and torch.equal(p2.offsets, want.offsets) and torch.equal(p2.n_tiles, want.n_tiles)
+        nt, total = int(want.n_tiles), int(want.offsets[-1])
+        assert torch.equal(p2.tile_expert[:nt], want.tile_expert[:nt]) and torch.equal(p2.tile_row0[:nt], want.tile_row0[:nt])
+        off = want.offsets.tolist()
+        for e in range(E):       # the same pairs per expert, in whatever order
+            assert sorted(p2.sorted_pair[off[e]:off[e + 1]].tolist()) == sorted(want.sorted_pair[off[e]:off[e + 1]].tolist())
+        assert total == int((i2 < E).sum())
     # without the correction the choice differs somewhere (the test's numbers show the mechanism)
-    idx0, _, _ = K.moe_router(h.to(DEV), Wr.to(DEV), None, n, False, top, groups, keep)
+    idx0, _, _, _ = K.moe_router(h.to(DEV), Wr.to(DEV), None, n, False, top, groups, keep)
     if n > top:
         assert not torch.equal(idx0, idx)
 
