@@ -170,10 +170,15 @@ class LLM:
 
     def model_info(self) -> ModelInfo:
         c = self.engine.config
+        # designs whose configuration gives sizes layer by layer: those of the first layer's parts
+        first = self.engine.model.blocks[self.engine.spec.order[0].layer]
+        mixer, ffn = first.mixer, first.ffn
         return ModelInfo(
             architecture=self.engine.spec.name, layers=len(self.engine.spec.order),
-            dimension=self.engine.spec.hidden_size, heads=getattr(c, "num_attention_heads", 0),
-            kv_heads=getattr(c, "num_key_value_heads", 0), ffn_dim=getattr(c, "intermediate_size", 0),
+            dimension=self.engine.spec.hidden_size,
+            heads=getattr(c, "num_attention_heads", None) or getattr(mixer, "num_heads", 0),
+            kv_heads=getattr(c, "num_key_value_heads", None) or getattr(mixer, "num_kv_heads", 0),
+            ffn_dim=getattr(c, "intermediate_size", None) or getattr(ffn, "intermediate_size", 0),
             vocab_size=self.engine.spec.vocab_size, context_len=self.engine.spec.max_positions)
 
 

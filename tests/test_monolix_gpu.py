@@ -498,7 +498,9 @@ def test_greedy_generation_through_the_entry_point(dirs):
                 k = next(i for i in range(12) if g[i] != want[i])
                 lg = P.forward(cfg, w, p + want[:k])[-1]
                 assert float(lg[want[k]] - lg[g[k]]) < 1e-4 * float(lg.abs().max()), (name, g, want)
-        assert llm.model_info().architecture == "Monolix"
+        info = llm.model_info()
+        assert info.architecture == "Monolix" and info.layers == len(cfg["layers"])
+        assert (info.heads, info.kv_heads) == (cfg["layers"][0]["mixer"]["heads"], cfg["layers"][0]["mixer"]["kv_heads"])
         out = llm.generate(prompts[:2], max_tokens=5, temperature=0.8, top_k=20, seed=3, ignore_eos=True)
         assert all(len(o) == 5 and all(0 <= t < cfg["vocab"] for t in o) for o in out)
 
