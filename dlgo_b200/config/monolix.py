@@ -2,7 +2,7 @@
 
 A Monolix model is a list of layers that norm AFTER the residual sum, each a grouped-query attention
 mixer whose values are its keys as projected, plus an optional mixture-of-experts feed-forward; a layer
-may run with the tensors of an earlier layer while keeping a cache of its own:
+may run with the tensors of another layer (earlier or later in the list) while keeping a cache of its own:
 
     {"architecture": "Monolix", "vocab": V, "width": d, "norm": {"eps": e}, "postln_alpha": a,
      "layers": [{"type": "attention",
@@ -145,13 +145,23 @@ class MonolixConfig:
             of = L.get("weights_of")
             if of is not None:
                 of = _as(of, "weights_of", int)
-                if not 0 <= of < i:
-                    raise ConfigError(f"config.json: {where}weights_of names layer {of}, which does not come before")
-                while layers[of].weights_of is not None:      # a chain ends at the layer that holds the tensors
-                    of = layers[of].weights_of
-                if (layers[of].mixer, layers[of].mlp) != (mixer, mlp):
-                    raise ConfigError(f"config.json: {where}uses the tensors of layer {of} but its sizes differ")
+                if not 0 <= of < len(layers_in) or of == i:
+                    raise ConfigError(f"config.json: {where}weights_of names layer {of}; it must name another layer")
             layers.append(MonolixLayer(kind, mixer, mlp, of))
+        # a chain of weights_of ends at the layer that holds the tensors (which may come later in the file)
+        for i, L in enumerate(layers):
+            of, seen = L.weights_of, {i}
+            while of is not None and layers[of].weights_of is not None:
+                if of in seen:
+                    raise ConfigError(f"config.json: layers[{i}].weights_of runs in a circle")
+                seen.add(of)
+                of = layers[of].weights_of
+            if of is not None:
+                if of in seen:
+                    raise ConfigError(f"config.json: layers[{i}].weights_of runs in a circle")
+                if (layers[of].mixer, layers[of].mlp) != (L.mixer, L.mlp):
+                    raise ConfigError(f"config.json: layers[{i}] uses the tensors of layer {of} but its sizes differ")
+                layers[i] = MonolixLayer(L.kind, L.mixer, L.mlp, of)
         vocab, width = _need(d, "vocab", int), _need(d, "width", int)
         if vocab <= 0 or width <= 0:
             raise ConfigError("config.json: 'vocab' and 'width' must be positive")
@@ -210,7 +220,6 @@ class MonolixConfig:
         order: List[RunEntry] = []
         for i, L in enumerate(self.layers):
             if L.weights_of is not None:
-                order.append(RunEntry(place[L.weights_of]))    # shared tensors, a cache of its own
                 continue
             mixer, pe = self._mixer_spec(L.mixer)
             if pe is not None:
@@ -226,9 +235,10 @@ class MonolixConfig:
                 connections["ffn_conn"] = scale
                 names.update({"ffn": "mlp.", "ffn_norm": "norm2", "ffn_conn": "ls2"})
             place[i] = len(layers)
-            order.append(RunEntry(place[i]))
             layers.append(LayerSpec(prefix=f"l{i}.", block="postnorm", mixer=mixer, ffn=ffn, norms=norms,
                                     names=names, connections=connections))
+        # every layer of the file is one run entry: shared tensors, a cache of its own
+        order = [RunEntry(place[i if L.weights_of is None else L.weights_of]) for i, L in enumerate(self.layers)]
         spec = ArchitectureSpec(
             name=self.architecture, hidden_size=d, vocab_size=self.vocab, max_positions=NO_CONTEXT_LIMIT,
             embedding=PartSpec("token_embedding", {"vocab_size": self.vocab, "hidden_size": d, "name": "embed"}),

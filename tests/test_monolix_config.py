@@ -51,6 +51,23 @@ def test_a_head_size_that_is_no_multiple_of_eight_is_laid_out_as_the_next_one():
     assert (needs[0].num_kv_heads, needs[0].head_dim) == (1, 24)
 
 
+def test_weights_of_may_name_a_later_layer_and_chains_end_at_the_holder():
+    c = copy.deepcopy(CONFIGS["R"])
+    c["layers"][0]["weights_of"] = 2            # 0 -> 2 -> 1: layer 1 holds the tensors
+    c["layers"][1].pop("weights_of")
+    c["layers"][2]["weights_of"] = 1
+    cfg = config_from_dict(c)
+    assert [L.weights_of for L in cfg.layers] == [1, None, 1]
+    spec = cfg.architecture_spec()
+    assert [ls.prefix for ls in spec.layers] == ["l1."] and [e.layer for e in spec.order] == [0, 0, 0]
+    w = make_weights(c, 3)
+    assert all(n.startswith("l1.") or "." not in n or n.startswith("final") for n in w)
+    assert P.weights_layer(c, 0) == 1 and P.weights_layer(c, 2) == 1
+    c["layers"][1]["weights_of"] = 0            # a circle
+    with pytest.raises(ConfigError):
+        config_from_dict(c)
+
+
 def test_expected_tensors():
     t = CausalLM(config_from_dict(CONFIGS["P"]).architecture_spec()).expected_tensors()
     shape = {n: tuple(ps.shape) for n, ps in t.items()}

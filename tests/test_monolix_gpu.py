@@ -341,6 +341,16 @@ def test_head_sizes_that_are_no_multiple_of_eight(dim, rot, dtype):
     assert_rows(torch.cat(got), ref, dtype, "prefill then decode")
 
 
+def test_a_layer_may_use_a_later_layer_s_tensors():
+    cfg = copy.deepcopy(CONFIGS["R"])
+    cfg["layers"][0]["weights_of"] = 2            # 0 -> 2 -> 1: layer 1 holds the tensors
+    cfg["layers"][1].pop("weights_of")
+    cfg["layers"][2]["weights_of"] = 1
+    w = make_weights(cfg, 4)
+    tokens = random_tokens(90, cfg["vocab"], 6)
+    assert_rows(run_whole(engine_of(cfg, w, "float32"), tokens), plain_of(cfg, w, tokens), "float32", "whole")
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_values_are_the_keys_as_projected(dtype):
     """What is summed is the key before norm and rotation, with its bias: an oracle that sums the normed and
