@@ -46,6 +46,10 @@ __device__ __forceinline__ float gt_act(float v, int act) {
   }
 }
 
+// Persistent: a few CTAs per SM, each walking the work items (row tile, block of BN columns) it is dealt
+// round-robin, columns first so that neighbouring CTAs read the same expert's weight tile at the same time.  The
+// loader runs ahead into the next item's tiles while the epilogue warps empty the accumulator, and the MMAs of the
+// next item start as soon as the accumulator has been read into registers.
 template <int BN>
 __global__ void __launch_bounds__(GT_THREADS)
 moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -56,17 +60,17 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   const int STAGES = p.stages;
   uint64_t* full = (uint64_t*)(smem + STAGES * STAGE);
   uint64_t* empty = full + STAGES;
-  uint64_t* accum = empty + STAGES;
-  uint32_t* tmem_slot = (uint32_t*)(accum + 1);
+  uint64_t* acc_full = empty + STAGES;
+  uint64_t* acc_empty = acc_full + 1;
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   pdl_wait();                       // the plan and the rows are written by earlier kernels of the step
-  const int tile = blockIdx.y;
-  if (tile >= *p.n_tiles) return;   // before anything is allocated
+  const int n_tiles = *p.n_tiles;
+  const int n_blocks = (p.N + BN - 1) / BN;
+  const int n_items = n_tiles * n_blocks;
+  if ((int)blockIdx.x >= n_items) return;   // before anything is allocated
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int e = p.tile_expert[tile], row0 = p.tile_row0[tile];
-  const int nr = min(GT_M, p.offsets[e + 1] - row0);
-  const int n0 = blockIdx.x * BN;
   const int nkb = (p.K + GT_K - 1) / GT_K;
 
   if (threadIdx.x == 0) {
@@ -74,7 +78,8 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    mbar_init(accum, 1);
+    mbar_init(acc_full, 1);
+    mbar_init(acc_empty, 4);        // one arrival per epilogue warp
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&map_a);
@@ -95,104 +100,106 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 
   if (warp == 0) {
     if (elect_one()) {
-      for (int i = 0; i < nkb; ++i) {
-        const int s = i % STAGES;
-        const uint32_t ph = (i / STAGES) & 1;
-        if (i >= STAGES && !mbar_wait(&empty[s], ph ^ 1, abort_flag)) break;
-        uint8_t* a_dst = smem + s * STAGE;
-        mbar_expect_tx(&full[s], STAGE);
-        tma_load_2d(a_dst, &map_a, &full[s], i * GT_K, row0);
-        tma_load_2d(a_dst + A_BYTES, &map_b, &full[s], i * GT_K, e * p.N + n0);
+      int it = 0;
+      bool live = true;
+      for (int item = blockIdx.x; item < n_items && live; item += gridDim.x) {
+        const int tile = item % n_tiles, nb = item / n_tiles;
+        const int e = p.tile_expert[tile], row0 = p.tile_row0[tile];
+        for (int i = 0; i < nkb; ++i, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (it >= STAGES && !mbar_wait(&empty[s], ph ^ 1, abort_flag)) { live = false; break; }
+          uint8_t* a_dst = smem + s * STAGE;
+          mbar_expect_tx(&full[s], STAGE);
+          tma_load_2d(a_dst, &map_a, &full[s], i * GT_K, row0);
+          tma_load_2d(a_dst + A_BYTES, &map_b, &full[s], i * GT_K, e * p.N + nb * BN);
+        }
       }
     }
   } else if (warp == 1) {
     if (elect_one()) {
       constexpr uint32_t idesc = umma_idesc_bf16(GT_M, BN);
-      for (int i = 0; i < nkb; ++i) {
-        const int s = i % STAGES;
-        const uint32_t ph = (i / STAGES) & 1;
-        if (!mbar_wait(&full[s], ph, abort_flag)) break;
+      int it = 0, j = 0;
+      bool live = true;
+      for (int item = blockIdx.x; item < n_items && live; item += gridDim.x, ++j) {
+        // the epilogue warps have read the previous item's accumulator into registers
+        if (j >= 1 && !mbar_wait(acc_empty, (j - 1) & 1, abort_flag)) break;
         tc_fence_after_sync();
-        const uint32_t a_addr = smem_u32(smem + s * STAGE);
-        const uint64_t da = umma_desc_k_sw128(a_addr);
-        const uint64_t db = umma_desc_k_sw128(a_addr + A_BYTES);
+        for (int i = 0; i < nkb; ++i, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full[s], ph, abort_flag)) { live = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + s * STAGE);
+          const uint64_t da = umma_desc_k_sw128(a_addr);
+          const uint64_t db = umma_desc_k_sw128(a_addr + A_BYTES);
 #pragma unroll
-        for (int k = 0; k < GT_K / GT_UMMA_K; ++k) umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (i | k) != 0);
-        umma_commit(&empty[s]);
+          for (int k = 0; k < GT_K / GT_UMMA_K; ++k) umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (i | k) != 0);
+          umma_commit(&empty[s]);
+        }
+        if (live) umma_commit(acc_full);
       }
-      umma_commit(accum);
     }
   } else {
     const int quarter = warp & 3;                 // warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31
     const int r_in = quarter * 32 + lane;
-    const bool ok = mbar_wait(accum, 0, abort_flag);
-    tc_fence_after_sync();
-    // The ring is idle by now (every MMA has read it): each epilogue warp lays 64 columns of its 32 rows out in
-    // its own corner of it, then writes them row by row, so that a store instruction covers whole 128-byte lines
-    // of a few rows instead of 16 bytes of each of 32 rows.
-    constexpr int LD = 68;                                   // floats per staged row (64 + 4: rows shift by 4 banks)
-    float* stg = (float*)smem + quarter * (32 * LD);
-    const int rows_w = min(32, max(0, nr - quarter * 32));   // rows of this warp that belong to the expert
-    long long my_dst = 0;
-    if (ok && lane < rows_w) my_dst = (p.o_scatter != nullptr ? p.o_scatter[row0 + r_in] : (row0 + r_in)) * p.ldo;
-    if (ok && rows_w > 0) {
+    int j = 0;
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++j) {
+      const int tile = item % n_tiles, nb = item / n_tiles;
+      const int e = p.tile_expert[tile], row0 = p.tile_row0[tile];
+      const int nr = min(GT_M, p.offsets[e + 1] - row0);
+      const int n0 = nb * BN;
+      const bool mine = r_in < nr;
+      long long dst_row = 0;
+      if (mine) dst_row = (p.o_scatter != nullptr ? p.o_scatter[row0 + r_in] : (row0 + r_in)) * p.ldo;
+      if (!mbar_wait(acc_full, j & 1, abort_flag)) break;
+      tc_fence_after_sync();
+      // a lane per row, 32 columns at a time straight from tensor memory to global memory (a row's 32 columns
+      // are 64 or 128 contiguous bytes); the accumulator is handed back as soon as its last columns are in registers
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN && n0 + c0 < p.N; c0 += 64) {
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          if (n0 + c0 + half * 32 < p.N) {                   // (uniform over the warp)
-            float v[32];
-            tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c0 + half * 32), v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              *reinterpret_cast<float4*>(stg + lane * LD + half * 32 + j) =
-                  make_float4(gt_act(v[j], p.act), gt_act(v[j + 1], p.act), gt_act(v[j + 2], p.act), gt_act(v[j + 3], p.act));
-          }
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        const bool last = c0 + 32 >= BN || n0 + c0 + 32 >= p.N;
+        if (n0 + c0 >= p.N) break;                // (uniform over the warp)
+        float v[32];
+        tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+        tmem_ld_wait();
+        if (last) {
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acc_empty);
         }
-        __syncwarp();
+        if (!mine) continue;
+#pragma unroll
+        for (int q = 0; q < 32; ++q) v[q] = gt_act(v[q], p.act);
         const int col = n0 + c0;
-        const int ncols = min(64, p.N - col);
         if (p.out_f32) {
-          const int sub = (lane & 15) * 4, rr = lane >> 4;   // 16 lanes a row, two rows an instruction
-#pragma unroll 1
-          for (int r = 0; r < 32; r += 2) {
-            const long long base = __shfl_sync(0xffffffffu, my_dst, r + rr);
-            if (r + rr < rows_w && sub < ncols) {
-              const float4 o = *reinterpret_cast<const float4*>(stg + (r + rr) * LD + sub);
-              float* dst = (float*)p.out + base + col + sub;
-              if (sub + 4 <= ncols && ((uintptr_t)dst & 15) == 0) {
-                *reinterpret_cast<float4*>(dst) = o;
-              } else {
-                const float e[4] = {o.x, o.y, o.z, o.w};
-                for (int j = 0; j < 4 && sub + j < ncols; ++j) dst[j] = e[j];
-              }
-            }
+          float* dst = (float*)p.out + dst_row + col;
+          if (col + 32 <= p.N && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+            for (int q = 0; q < 32; q += 4) *reinterpret_cast<float4*>(dst + q) = make_float4(v[q], v[q + 1], v[q + 2], v[q + 3]);
+          } else {
+#pragma unroll
+            for (int q = 0; q < 32; ++q)
+              if (col + q < p.N) dst[q] = v[q];
           }
         } else {
-          const int sub = (lane & 7) * 8, rr = lane >> 3;    // 8 lanes a row, four rows an instruction
-#pragma unroll 1
-          for (int r = 0; r < 32; r += 4) {
-            const long long base = __shfl_sync(0xffffffffu, my_dst, r + rr);
-            if (r + rr < rows_w && sub < ncols) {
-              const float4 a = *reinterpret_cast<const float4*>(stg + (r + rr) * LD + sub);
-              const float4 b = *reinterpret_cast<const float4*>(stg + (r + rr) * LD + sub + 4);
-              __nv_bfloat16* dst = (__nv_bfloat16*)p.out + base + col + sub;
-              if (sub + 8 <= ncols && ((uintptr_t)dst & 15) == 0) {
-                uint4 o;
-                __nv_bfloat162 b0 = __floats2bfloat162_rn(a.x, a.y), b1 = __floats2bfloat162_rn(a.z, a.w);
-                __nv_bfloat162 b2 = __floats2bfloat162_rn(b.x, b.y), b3 = __floats2bfloat162_rn(b.z, b.w);
-                o.x = *reinterpret_cast<unsigned*>(&b0); o.y = *reinterpret_cast<unsigned*>(&b1);
-                o.z = *reinterpret_cast<unsigned*>(&b2); o.w = *reinterpret_cast<unsigned*>(&b3);
-                *reinterpret_cast<uint4*>(dst) = o;
-              } else {
-                const float e[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-                for (int j = 0; j < 8 && sub + j < ncols; ++j) dst[j] = __float2bfloat16_rn(e[j]);
-              }
+          __nv_bfloat16* dst = (__nv_bfloat16*)p.out + dst_row + col;
+          if (col + 32 <= p.N && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+            for (int q = 0; q < 32; q += 8) {
+              uint4 o;
+              __nv_bfloat162 b0 = __floats2bfloat162_rn(v[q], v[q + 1]), b1 = __floats2bfloat162_rn(v[q + 2], v[q + 3]);
+              __nv_bfloat162 b2 = __floats2bfloat162_rn(v[q + 4], v[q + 5]), b3 = __floats2bfloat162_rn(v[q + 6], v[q + 7]);
+              o.x = *reinterpret_cast<unsigned*>(&b0); o.y = *reinterpret_cast<unsigned*>(&b1);
+              o.z = *reinterpret_cast<unsigned*>(&b2); o.w = *reinterpret_cast<unsigned*>(&b3);
+              *reinterpret_cast<uint4*>(dst + q) = o;
             }
+          } else {
+#pragma unroll
+            for (int q = 0; q < 32; ++q)
+              if (col + q < p.N) dst[q] = __float2bfloat16_rn(v[q]);
           }
         }
-        __syncwarp();
       }
     }
   }
@@ -285,7 +292,22 @@ int launch_grouped(const CUtensorMap& ma, const CUtensorMap& mb, GroupedTcParams
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  dim3 grid((p.N + BN - 1) / BN, max_tiles);
+  // as many CTAs as are resident at once (what shared memory allows per SM), or fewer where the items are fewer
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  int per_sm = (227 * 1024) / (smem + 1024);
+  const int by_tmem = 512 / BN;
+  if (per_sm > by_tmem) per_sm = by_tmem;
+  if (per_sm < 1) per_sm = 1;
+  static const int per_sm_env = [] { const char* e = getenv("DLGO_MOE_TC_CTAS_PER_SM"); return e ? atoi(e) : 0; }();
+  if (per_sm_env > 0 && per_sm_env < per_sm) per_sm = per_sm_env;
+  const long long items = (long long)max_tiles * ((p.N + BN - 1) / BN);
+  const long long want = (long long)sms * per_sm;
+  dim3 grid((unsigned)(items < want ? items : want));
   launch_kernel(moe_gemm_tc_kernel<BN>, grid, dim3(GT_THREADS), (size_t)smem, stream, ma, mb, p);
   return launch_status();
 }
