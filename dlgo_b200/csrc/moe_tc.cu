@@ -1,4 +1,5 @@
-// Grouped contraction of routed experts on the tensor cores (tcgen05), for prompts in bfloat16.
+// Grouped contraction of routed experts on the tensor cores (tcgen05), in bfloat16: prompts, and decode steps of
+// a couple of dozen (token, choice) pairs and more.
 //
 // Rows are (token, choice) pairs sorted by expert (the plan of moe.cu, tiles of 128 rows): tile t belongs to
 // expert e = tile_expert[t] and covers sorted rows row0 .. row0 + 127, of which the first
@@ -12,8 +13,9 @@
 // experts' weights stacked [experts * N, K].  Both operands arrive by TMA (128-byte swizzle, zero fill beyond
 // the tensors, no multicast) in a shared-memory ring; one thread issues tcgen05.mma into a 128 x BN fp32
 // accumulator in tensor memory; four warps read it back (a lane per row), apply the activation in fp32 and
-// store a row's 32 columns at a time: in the activation type at row r, or fp32 at row o_scatter[r].
-// Warp 0 loads, warp 1 issues MMAs, warps 2-5 are the epilogue.  Every wait is bounded and sets an error word.
+// store a row's 32 columns at a time: in the activation type or fp32, at row r or at row o_scatter[r].
+// Warp 0 loads, warp 1 issues MMAs, warps 2-5 are the epilogue.  CTAs are persistent (a few per SM, each walking
+// the items it is dealt).  Every wait is bounded and sets an error word.
 #include "common.cuh"
 #include "tcgen05.cuh"
 
@@ -275,8 +277,10 @@ int launch_grouped(const CUtensorMap& ma, const CUtensorMap& mb, GroupedTcParams
   // B200 (width 2,048, 56 experts of 1,024, 8 chosen; prompt of 2,048 tokens / decode step at batch 8, ms): tiles 256
   // wide with 100 KB 3.29 / 0.734, with 150 KB 3.91 / 0.801; 128 wide with 100 KB 3.32 / 0.668, with 66 KB (two
   // stages, three CTAs an SM) 3.16 / 0.629; 64 wide with 75 KB (three stages, three CTAs an SM) 3.29 / 0.597.  So
-  // prompts take 128 x 128 tiles and steps of few rows 128 x 64.  DLGO_MOE_TC_RING_KB and DLGO_MOE_TC_BN (64, 128,
-  // 256) override.
+  // prompts take 128 x 128 tiles and steps of few rows 128 x 64 (measured with one tile per CTA; with persistent
+  // CTAs the order is the same: prompt tok/s / decode ms, 128 wide two stages 689 k / 0.578, 256 wide two stages 670 k
+  // / 0.644, 64 wide three stages 658 k / 0.542).  DLGO_MOE_TC_RING_KB, DLGO_MOE_TC_BN (64, 128, 256) and
+  // DLGO_MOE_TC_CTAS_PER_SM override.
   static const int ring_env = [] { const char* e = getenv("DLGO_MOE_TC_RING_KB"); return e ? atoi(e) : 0; }();
   const int ring_kb = ring_env > 0 ? ring_env : ring_default_kb;
   int stages = (ring_kb * 1024) / STAGE;
