@@ -597,7 +597,7 @@ def scaled_add_rmsnorm(x: torch.Tensor, y: Optional[torch.Tensor], layer_scale: 
 
 
 # ------------------------------------------------------------------ routed experts
-MOE_FEW_ROWS, MOE_TILE_ROWS, MOE_TC_ROWS = 8, 64, 128      # rows per tile of the grouped contractions
+MOE_FEW_ROWS, MOE_TILE_ROWS, MOE_TC_ROWS, MOE_TC_PAIR_ROWS = 8, 64, 128, 256      # rows per tile of the grouped contractions
 
 
 def moe_router(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], n_outputs: int,
@@ -722,16 +722,17 @@ def moe_gemm_tc(plan: MoEPlan, a: torch.Tensor, w: torch.Tensor, out: torch.Tens
     pair(r)."""
     _need(a, torch.bfloat16, "a")
     _need(w, torch.bfloat16, "w")
-    if plan.tile_rows != MOE_TC_ROWS or w.dim() != 3 or a.dim() != 2 or out.dim() != 2 or out.stride(1) != 1:
-        raise KernelError("moe_gemm_tc: a plan with tiles of 128 rows, a and out 2-D, w [experts, N, K]")
+    if (plan.tile_rows not in (MOE_TC_ROWS, MOE_TC_PAIR_ROWS) or w.dim() != 3 or a.dim() != 2 or out.dim() != 2 or
+            out.stride(1) != 1):
+        raise KernelError("moe_gemm_tc: a plan with tiles of 128 rows (or 256: CTA pairs), a and out 2-D, w [experts, N, K]")
     E, N, Kd = w.shape
     if a.shape[1] != Kd or out.shape[1] != N or out.dtype not in (torch.float32, torch.bfloat16):
         raise KernelError("moe_gemm_tc: shapes or types do not fit")
     st = _lib("moe_tc").dlgo_moe_gemm_tc(
         _ptr(a), _ll(a.shape[0]), _ll(a.stride(0)), _ptr(w), _i(E), _ptr(out), _ll(out.stride(0)),
         _ptr(plan.sorted_pair if scatter else None), _ptr(plan.offsets), _ptr(plan.tile_expert), _ptr(plan.tile_row0),
-        _ptr(plan.n_tiles), _i(plan.max_tiles), _i(N), _i(Kd), _i(act), _i(1 if out.dtype == torch.float32 else 0),
-        _stream())
+        _ptr(plan.n_tiles), _i(plan.max_tiles), _i(plan.tile_rows), _i(N), _i(Kd), _i(act),
+        _i(1 if out.dtype == torch.float32 else 0), _stream())
     _check(st, "moe_gemm_tc")
     return out
 

@@ -220,6 +220,182 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   }
 }
 
+// The same on CTA pairs (cta_group::2) for prompts: a pair takes TWO row tiles of one expert (the plan's tiles have 256
+// rows; CTA r of the pair owns rows 128 r .. 128 r + 127 of it) against ONE weight tile of BN columns of which each
+// CTA fetches half, so a k-block costs a CTA 16 KB of rows and BN / 2 x 128 bytes of weights for 128 x BN x 64 of
+// MMA work: twice the FLOPs per operand byte of a single CTA on a 128 x 128 tile.  The leader's MMA warp issues for
+// both; barriers as in the dense pair kernel: `full` counts both CTAs' bytes in the leader, `empty` and `acc_full`
+// are signalled in both CTAs by one commit, `acc_empty` collects all 256 epilogue threads in the leader.  A half
+// without rows of the expert (the expert's last rows fill only the first half) fetches no rows and stores nothing.
+template <int BN>
+__global__ void __launch_bounds__(GT_THREADS)
+moe_gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                        const __grid_constant__ GroupedTcParams p) {
+  constexpr int HALF_N = BN / 2;
+  constexpr int A_BYTES = GT_M * GT_K * 2, B_BYTES = HALF_N * GT_K * 2, STAGE = A_BYTES + B_BYTES;
+  extern __shared__ uint8_t gt_smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)gt_smem_raw + 1023) & ~(uintptr_t)1023);
+  const int STAGES = p.stages;
+  uint64_t* full = (uint64_t*)(smem + STAGES * STAGE);     // used in the leader only
+  uint64_t* empty = full + STAGES;                          // local in each CTA
+  uint64_t* acc_full = empty + STAGES;                      // local in each CTA
+  uint64_t* acc_empty = acc_full + 1;                       // used in the leader only (256 arrivals)
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 1);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  pdl_wait();                       // the plan and the rows are written by earlier kernels of the step
+  const int n_tiles = *p.n_tiles;
+  const int n_blocks = (p.N + BN - 1) / BN;
+  const int n_items = n_tiles * n_blocks;
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  if (pair >= n_items) return;      // both CTAs of the pair, before anything is allocated
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int nkb = (p.K + GT_K - 1) / GT_K;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(acc_full, 1);
+    mbar_init(acc_empty, 256);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, BN);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();               // both CTAs' barriers exist before anything arrives on them remotely
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  // (dependents only now: see the single-CTA kernel)
+  pdl_launch_dependents();
+
+  if (warp == 0) {
+    if (elect_one()) {
+      int it = 0;
+      bool live = true;
+      for (int item = pair; item < n_items && live; item += n_pairs) {
+        const int tile = item % n_tiles, nb = item / n_tiles;
+        const int e = p.tile_expert[tile], row0 = p.tile_row0[tile];
+        const int rows_left = p.offsets[e + 1] - row0;                 // of the expert, from this tile on
+        const bool peer_has = rows_left > GT_M, mine_has = rank == 0 || peer_has;
+        for (int i = 0; i < nkb; ++i, ++it) {
+          const int s = it % STAGES;
+          if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag)) { live = false; break; }
+          uint8_t* a_dst = smem + s * STAGE;
+          // the leader's barrier counts the bytes of both CTAs' loads
+          const uint32_t bar = map_to_cta(smem_u32(&full[s]), 0);
+          if (rank == 0) mbar_expect_tx(&full[s], (peer_has ? 2 * A_BYTES : A_BYTES) + 2 * B_BYTES);
+          if (mine_has) tma_load_2d_pair(a_dst, &map_a, bar, i * GT_K, row0 + (int)rank * GT_M);
+          tma_load_2d_pair(a_dst + A_BYTES, &map_b, bar, i * GT_K, e * p.N + nb * BN + (int)rank * HALF_N);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (rank == 0 && elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16(2 * GT_M, BN);
+      int it = 0, j = 0;
+      bool live = true;
+      for (int item = pair; item < n_items && live; item += n_pairs, ++j) {
+        if (j >= 1 && !mbar_wait(acc_empty, (j - 1) & 1, abort_flag)) break;
+        tc_fence_after_sync();
+        for (int i = 0; i < nkb; ++i, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&full[s], (it / STAGES) & 1, abort_flag)) { live = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + s * STAGE);
+          const uint64_t da = umma_desc_k_sw128(a_addr);
+          const uint64_t db = umma_desc_k_sw128(a_addr + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < GT_K / GT_UMMA_K; ++k) umma_bf16_pair(tmem_base, da + 2 * k, db + 2 * k, idesc, (i | k) != 0);
+          umma_commit_pair(&empty[s]);       // both CTAs may refill the stage
+        }
+        umma_commit_pair(acc_full);          // both CTAs' epilogues may read the accumulator (or leave, if not live)
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r_in = quarter * 32 + lane;
+    const uint32_t acc_empty_leader = map_to_cta(smem_u32(acc_empty), 0);
+    int j = 0;
+    for (int item = pair; item < n_items; item += n_pairs, ++j) {
+      const int tile = item % n_tiles, nb = item / n_tiles;
+      const int e = p.tile_expert[tile], row0 = p.tile_row0[tile] + (int)rank * GT_M;
+      const int nr = min(GT_M, p.offsets[e + 1] - row0);             // may be <= 0 for the second half
+      const int n0 = nb * BN;
+      const bool mine = r_in < nr;
+      long long dst_row = 0;
+      if (mine) dst_row = (p.o_scatter != nullptr ? p.o_scatter[row0 + r_in] : (row0 + r_in)) * p.ldo;
+      if (!mbar_wait(acc_full, j & 1, abort_flag)) break;
+      tc_fence_after_sync();
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        const bool last = c0 + 32 >= BN || n0 + c0 + 32 >= p.N;
+        if (n0 + c0 >= p.N) break;                // (uniform over the warp)
+        float v[32];
+        tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+        tmem_ld_wait();
+        if (last) {
+          tc_fence_before_sync();
+          mbar_arrive_cluster(acc_empty_leader);   // every epilogue thread of both CTAs
+        }
+        if (!mine) continue;
+#pragma unroll
+        for (int q = 0; q < 32; ++q) v[q] = gt_act(v[q], p.act);
+        const int col = n0 + c0;
+        if (p.out_f32) {
+          float* dst = (float*)p.out + dst_row + col;
+          if (col + 32 <= p.N && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+            for (int q = 0; q < 32; q += 4) *reinterpret_cast<float4*>(dst + q) = make_float4(v[q], v[q + 1], v[q + 2], v[q + 3]);
+          } else {
+#pragma unroll
+            for (int q = 0; q < 32; ++q)
+              if (col + q < p.N) dst[q] = v[q];
+          }
+        } else {
+          __nv_bfloat16* dst = (__nv_bfloat16*)p.out + dst_row + col;
+          if (col + 32 <= p.N && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+            for (int q = 0; q < 32; q += 8) {
+              uint4 o;
+              __nv_bfloat162 b0 = __floats2bfloat162_rn(v[q], v[q + 1]), b1 = __floats2bfloat162_rn(v[q + 2], v[q + 3]);
+              __nv_bfloat162 b2 = __floats2bfloat162_rn(v[q + 4], v[q + 5]), b3 = __floats2bfloat162_rn(v[q + 6], v[q + 7]);
+              o.x = *reinterpret_cast<unsigned*>(&b0); o.y = *reinterpret_cast<unsigned*>(&b1);
+              o.z = *reinterpret_cast<unsigned*>(&b2); o.w = *reinterpret_cast<unsigned*>(&b3);
+              *reinterpret_cast<uint4*>(dst + q) = o;
+            }
+          } else {
+#pragma unroll
+            for (int q = 0; q < 32; ++q)
+              if (col + q < p.N) dst[q] = __float2bfloat16_rn(v[q]);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();               // nobody leaves while the other CTA may still signal or be read
+  if (*abort_flag) {
+    if (threadIdx.x == 0) atomicExch(&g_moe_tc_error, 1);
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, BN);
+  }
+}
+
 // Rows of the step's tokens in sorted pair order: dst[r] = src[pair(r) / div] for the r < offsets[experts] rows
 // that belong to an expert (16 bytes per thread and step).
 __global__ void __launch_bounds__(256)
@@ -316,6 +492,36 @@ int launch_grouped(const CUtensorMap& ma, const CUtensorMap& mb, GroupedTcParams
   return launch_status();
 }
 
+int launch_grouped_pair(const CUtensorMap& ma, const CUtensorMap& mb, GroupedTcParams p, int max_tiles,
+                        cudaStream_t stream) {
+  constexpr int BN = 256;
+  constexpr int STAGE = (GT_M + BN / 2) * GT_K * 2;
+  static const int ring_kb = [] { const char* e = getenv("DLGO_MOE_TC_PAIR_RING_KB"); return e ? atoi(e) : 96; }();
+  int stages = (ring_kb * 1024) / STAGE;
+  if (stages > 8) stages = 8;
+  if (stages < 2) stages = 2;
+  p.stages = stages;
+  const int smem = stages * STAGE + 1024 + 256;
+  if (smem > 227 * 1024) return DLGO_ERR_SIZE;
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaError_t e = cudaFuncSetAttribute(moe_gemm_tc_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) { sms = 0; return (int)e; }
+  }
+  int per_sm = (227 * 1024) / (smem + 1024);
+  if (per_sm > 512 / BN) per_sm = 512 / BN;
+  if (per_sm < 1) per_sm = 1;
+  const long long items = (long long)max_tiles * ((p.N + BN - 1) / BN);
+  long long pairs = (long long)sms * per_sm / 2;
+  if (items < pairs) pairs = items;
+  launch_kernel_cluster(moe_gemm_tc_pair_kernel<BN>, dim3((unsigned)(2 * pairs)), dim3(GT_THREADS), (size_t)smem, stream,
+                        dim3(2, 1, 1), ma, mb, p);
+  return launch_status();
+}
+
 }  // namespace
 }  // namespace dlgo
 
@@ -325,14 +531,25 @@ using namespace dlgo;
 DLGO_EXPORT int dlgo_moe_gemm_tc_takes(int N, int K) { return (N > 0 && K > 0 && K % 8 == 0) ? 1 : 0; }
 
 // A [a_rows, K] bf16 (row stride lda) in sorted row order; W [experts * N, K] bf16 contiguous; the plan's tiles
-// have 128 rows.  out: bf16 or fp32 (out_f32), row stride ldo, rows r or o_scatter[r].
+// have 128 rows (one CTA per tile at a time) or 256 (CTA pairs).  out: bf16 or fp32 (out_f32), row stride ldo, rows r
+// or o_scatter[r].
 DLGO_EXPORT int dlgo_moe_gemm_tc(const void* A, long long a_rows, long long lda, const void* W, int experts, void* out,
                                  long long ldo, const int* o_scatter, const int* offsets, const int* tile_expert,
-                                 const int* tile_row0, const int* n_tiles, int max_tiles, int N, int K, int act,
-                                 int out_f32, cudaStream_t stream) {
+                                 const int* tile_row0, const int* n_tiles, int max_tiles, int tile_rows, int N, int K,
+                                 int act, int out_f32, cudaStream_t stream) {
   if (max_tiles <= 0 || max_tiles > 65535 || a_rows <= 0 || experts <= 0) return DLGO_ERR_SIZE;
   if (!dlgo_moe_gemm_tc_takes(N, K)) return DLGO_ERR_SIZE;
   CUtensorMap ma, mb;
+  if (tile_rows == 256) {
+    // CTA pairs: each CTA fetches its 128 rows and half of a weight tile of 256 columns
+    int st = make_map(&ma, A, a_rows, K, lda, GT_M);
+    if (st != DLGO_OK) return st;
+    st = make_map(&mb, W, (long long)experts * N, K, K, 128);
+    if (st != DLGO_OK) return st;
+    GroupedTcParams p{offsets, tile_expert, tile_row0, n_tiles, o_scatter, out, ldo, out_f32, act, N, K, 0};
+    return launch_grouped_pair(ma, mb, p, max_tiles, stream);
+  }
+  if (tile_rows != GT_M) return DLGO_ERR_SIZE;
   static const int force_bn = [] { const char* e = getenv("DLGO_MOE_TC_BN"); return e ? atoi(e) : 0; }();
   const int bn = force_bn == 64 || force_bn == 128 || force_bn == 256 ? force_bn : (a_rows <= 2048 ? 64 : 128);
   int st = make_map(&ma, A, a_rows, K, lda, GT_M);

@@ -38,6 +38,8 @@ _TENSOR_CORES = os.environ.get("DLGO_MOE_TC", "1") != "0"       # 0: the fp32-pi
 # 0.662; batch 2, 0.620 / 0.694; batch 4, 0.745 / 0.717; batch 8, 0.880 / 0.735; batch 32, 1.58 / 0.894.
 # With experts of a megabyte (width 1,024, experts of 512) the 8-row tiles still win at 32 pairs: 0.372 / 0.420.
 _TC_MIN_PAIRS = int(os.environ.get("DLGO_MOE_TC_MIN_PAIRS", 0))      # 0: 24, or 128 for experts below 2 MB
+# prompts (more than 2,048 pairs): CTA pairs on two row tiles of an expert that share one weight tile
+_TC_PAIRS = os.environ.get("DLGO_MOE_TC_PAIR", "0") != "0"
 
 
 class RoutedExperts(FeedForward):
@@ -126,7 +128,8 @@ class RoutedExperts(FeedForward):
         tc_from = _TC_MIN_PAIRS or (24 if self.intermediate_size * self.hidden_size >= (1 << 20) else 128)
         on_tc = self.on_tensor_cores and pairs >= tc_from
         few = pairs <= _FEW_PAIRS_PER_EXPERT * max(self.num_experts, 1)
-        tile_rows = K.MOE_TC_ROWS if on_tc else (K.MOE_FEW_ROWS if few else K.MOE_TILE_ROWS)
+        tile_rows = ((K.MOE_TC_PAIR_ROWS if _TC_PAIRS and pairs > 2048 else K.MOE_TC_ROWS) if on_tc else
+                     (K.MOE_FEW_ROWS if few else K.MOE_TILE_ROWS))
         idx, wt, gate, plan = K.moe_router(x, self.w_router, self.b_choice, self.n_outputs, self.shared_gate, self.top,
                                            self.group_count, self.group_keep, self.sigmoid_scores, self.renormalize,
                                            plan=(self.num_experts, tile_rows))

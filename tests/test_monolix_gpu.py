@@ -234,23 +234,25 @@ def test_experts_on_the_tensor_cores(T, d, ff, E, ident, top):
     K.moe_gemm(ref_plan, h, up, hid_ref, top, False, K.ACT_RELU2)
     out_ref = torch.zeros(T * top, d, device=DEV)
     K.moe_gemm(ref_plan, hid_ref, down, out_ref, None, True, K.ACT_NONE)
-    plan = K.moe_plan(idx, E, K.MOE_TC_ROWS)
-    rows = K.moe_gather_rows(plan, h, top)
-    hid = torch.full((T * top, ff), float("nan"), dtype=torch.bfloat16, device=DEV)
-    K.moe_gemm_tc(plan, rows, up, hid, False, K.ACT_RELU2)
-    out = torch.zeros(T * top, d, device=DEV)
-    K.moe_gemm_tc(plan, hid, down, out, True, K.ACT_NONE)
-    K.check_device_errors()
-    total = int(plan.offsets[-1])
-    assert total == int((idx < E).sum())
-    # sorted rows of the two plans differ in order within an expert: compare through the pair numbers
-    a = torch.zeros(T * top, ff, device=DEV)
-    a[plan.sorted_pair[:total].long()] = hid[:total].float()
-    b = torch.zeros(T * top, ff, device=DEV)
-    b[ref_plan.sorted_pair[:total].long()] = hid_ref[:total].float()
-    assert torch.isfinite(hid[:total].float()).all()
-    assert torch.allclose(a, b, rtol=2e-2, atol=2e-2 * float(b.abs().max()))
-    assert torch.allclose(out, out_ref, rtol=3e-2, atol=3e-2 * float(out_ref.abs().max())), float((out - out_ref).abs().max())
+    for tile_rows in (K.MOE_TC_ROWS, K.MOE_TC_PAIR_ROWS):       # one CTA per tile at a time; CTA pairs on two tiles
+        plan = K.moe_plan(idx, E, tile_rows)
+        rows = K.moe_gather_rows(plan, h, top)
+        hid = torch.full((T * top, ff), float("nan"), dtype=torch.bfloat16, device=DEV)
+        K.moe_gemm_tc(plan, rows, up, hid, False, K.ACT_RELU2)
+        out = torch.zeros(T * top, d, device=DEV)
+        K.moe_gemm_tc(plan, hid, down, out, True, K.ACT_NONE)
+        K.check_device_errors()
+        total = int(plan.offsets[-1])
+        assert total == int((idx < E).sum())
+        # sorted rows of the two plans differ in order within an expert: compare through the pair numbers
+        a = torch.zeros(T * top, ff, device=DEV)
+        a[plan.sorted_pair[:total].long()] = hid[:total].float()
+        b = torch.zeros(T * top, ff, device=DEV)
+        b[ref_plan.sorted_pair[:total].long()] = hid_ref[:total].float()
+        assert torch.isfinite(hid[:total].float()).all()
+        assert torch.allclose(a, b, rtol=2e-2, atol=2e-2 * float(b.abs().max())), tile_rows
+        assert torch.allclose(out, out_ref, rtol=3e-2, atol=3e-2 * float(out_ref.abs().max())), \
+            (tile_rows, float((out - out_ref).abs().max()))
 
 
 # ---------------------------------------------- one layer: a key that carries the answer
