@@ -37,6 +37,7 @@ struct GroupedTcParams {
   void* out;
   long long ldo;
   int out_f32, act, N, K, stages;
+  int nacc;                 // accumulators per CTA in tensor memory (1 or 2; the persistent single-CTA kernel)
 };
 
 __device__ __forceinline__ float gt_act(float v, int act) {
@@ -62,9 +63,10 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   const int STAGES = p.stages;
   uint64_t* full = (uint64_t*)(smem + STAGES * STAGE);
   uint64_t* empty = full + STAGES;
-  uint64_t* acc_full = empty + STAGES;
-  uint64_t* acc_empty = acc_full + 1;
-  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 1);
+  uint64_t* acc_full = empty + STAGES;      // [2]
+  uint64_t* acc_empty = acc_full + 2;       // [2]
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+  const int NACC = p.nacc;                  // with two, the MMAs of the next item run under this item's epilogue
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   pdl_wait();                       // the plan and the rows are written by earlier kernels of the step
@@ -80,15 +82,17 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    mbar_init(acc_full, 1);
-    mbar_init(acc_empty, 4);        // one arrival per epilogue warp
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+    }
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&map_a);
     tma_prefetch_desc(&map_b);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, BN);
+    tmem_alloc(tmem_slot, NACC * BN);
     tmem_relinquish();
   }
   tc_fence_before_sync();
@@ -124,9 +128,11 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       int it = 0, j = 0;
       bool live = true;
       for (int item = blockIdx.x; item < n_items && live; item += gridDim.x, ++j) {
-        // the epilogue warps have read the previous item's accumulator into registers
-        if (j >= 1 && !mbar_wait(acc_empty, (j - 1) & 1, abort_flag)) break;
+        // the epilogue warps have read this accumulator's previous item into registers
+        const int b = NACC == 2 ? (j & 1) : 0, u = NACC == 2 ? (j >> 1) : j;
+        if (u >= 1 && !mbar_wait(&acc_empty[b], (u - 1) & 1, abort_flag)) break;
         tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(b * BN);
         for (int i = 0; i < nkb; ++i, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -136,10 +142,10 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
           const uint64_t da = umma_desc_k_sw128(a_addr);
           const uint64_t db = umma_desc_k_sw128(a_addr + A_BYTES);
 #pragma unroll
-          for (int k = 0; k < GT_K / GT_UMMA_K; ++k) umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (i | k) != 0);
+          for (int k = 0; k < GT_K / GT_UMMA_K; ++k) umma_bf16(tmem_d, da + 2 * k, db + 2 * k, idesc, (i | k) != 0);
           umma_commit(&empty[s]);
         }
-        if (live) umma_commit(acc_full);
+        if (live) umma_commit(&acc_full[b]);
       }
     }
   } else {
@@ -154,8 +160,10 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       const bool mine = r_in < nr;
       long long dst_row = 0;
       if (mine) dst_row = (p.o_scatter != nullptr ? p.o_scatter[row0 + r_in] : (row0 + r_in)) * p.ldo;
-      if (!mbar_wait(acc_full, j & 1, abort_flag)) break;
+      const int b = NACC == 2 ? (j & 1) : 0, u = NACC == 2 ? (j >> 1) : j;
+      if (!mbar_wait(&acc_full[b], u & 1, abort_flag)) break;
       tc_fence_after_sync();
+      const uint32_t tmem_d = tmem_base + (uint32_t)(b * BN);
       // a lane per row, 32 columns at a time straight from tensor memory to global memory (a row's 32 columns
       // are 64 or 128 contiguous bytes); the accumulator is handed back as soon as its last columns are in registers
 #pragma unroll 1
@@ -163,12 +171,12 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         const bool last = c0 + 32 >= BN || n0 + c0 + 32 >= p.N;
         if (n0 + c0 >= p.N) break;                // (uniform over the warp)
         float v[32];
-        tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+        tmem_ld_32x32(tmem_d + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
         tmem_ld_wait();
         if (last) {
           tc_fence_before_sync();
           __syncwarp();
-          if (lane == 0) mbar_arrive(acc_empty);
+          if (lane == 0) mbar_arrive(&acc_empty[b]);
         }
         if (!mine) continue;
 #pragma unroll
@@ -216,7 +224,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   }
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, BN);
+    tmem_dealloc(tmem_base, NACC * BN);
   }
 }
 
@@ -479,8 +487,13 @@ int launch_grouped(const CUtensorMap& ma, const CUtensorMap& mb, GroupedTcParams
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   }
+  // two accumulators (the next item's MMAs under this item's epilogue) where tensor memory still allows three CTAs
+  // per SM, i.e. on the 64-wide tiles of small steps: 0.545 -> 0.535 ms a decode step at batch 8; on 128-wide tiles
+  // they cost a resident CTA and prompts lose (690 k -> 671 k tok/s).  DLGO_MOE_TC_NACC (1, 2) overrides.
+  static const int nacc_env = [] { const char* e = getenv("DLGO_MOE_TC_NACC"); return e ? atoi(e) : 0; }();
+  p.nacc = BN > 128 ? 1 : (nacc_env == 1 || nacc_env == 2 ? nacc_env : (BN == 64 ? 2 : 1));
   int per_sm = (227 * 1024) / (smem + 1024);
-  const int by_tmem = 512 / BN;
+  const int by_tmem = 512 / (p.nacc * BN);
   if (per_sm > by_tmem) per_sm = by_tmem;
   if (per_sm < 1) per_sm = 1;
   static const int per_sm_env = [] { const char* e = getenv("DLGO_MOE_TC_CTAS_PER_SM"); return e ? atoi(e) : 0; }();
@@ -546,7 +559,7 @@ DLGO_EXPORT int dlgo_moe_gemm_tc(const void* A, long long a_rows, long long lda,
     if (st != DLGO_OK) return st;
     st = make_map(&mb, W, (long long)experts * N, K, K, 128);
     if (st != DLGO_OK) return st;
-    GroupedTcParams p{offsets, tile_expert, tile_row0, n_tiles, o_scatter, out, ldo, out_f32, act, N, K, 0};
+    GroupedTcParams p{offsets, tile_expert, tile_row0, n_tiles, o_scatter, out, ldo, out_f32, act, N, K, 0, 1};
     return launch_grouped_pair(ma, mb, p, max_tiles, stream);
   }
   if (tile_rows != GT_M) return DLGO_ERR_SIZE;
@@ -556,7 +569,7 @@ DLGO_EXPORT int dlgo_moe_gemm_tc(const void* A, long long a_rows, long long lda,
   if (st != DLGO_OK) return st;
   st = make_map(&mb, W, (long long)experts * N, K, K, bn);
   if (st != DLGO_OK) return st;
-  GroupedTcParams p{offsets, tile_expert, tile_row0, n_tiles, o_scatter, out, ldo, out_f32, act, N, K, 0};
+  GroupedTcParams p{offsets, tile_expert, tile_row0, n_tiles, o_scatter, out, ldo, out_f32, act, N, K, 0, 1};
   if (bn == 256) return launch_grouped<256>(ma, mb, p, max_tiles, 100, stream);
   if (bn == 64) return launch_grouped<64>(ma, mb, p, max_tiles, 75, stream);
   return launch_grouped<128>(ma, mb, p, max_tiles, 66, stream);
